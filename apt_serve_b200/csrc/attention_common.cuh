@@ -1,0 +1,102 @@
+// Work planning, scratch layout and launch declarations shared by the K/V-path
+// and hidden-path decode attention kernels.
+//
+// A decode batch is cut into CHUNKS of kChunkTokens consecutive tokens of one
+// request.  Every chunk of a K/V-cached request is streamed by warps of the
+// K/V kernel (one warp per head); every chunk of a hidden-cached request is one
+// 128-row M tile of the re-projection GEMM.  Each (chunk, head) leaves a softmax
+// partial (running max and sum in the log2 domain, un-normalised fp32
+// accumulator) in the scratch buffer; a combine kernel merges a request's
+// partials in chunk order, so the result does not depend on scheduling.
+#pragma once
+
+#include "aps_common.cuh"
+
+namespace aps {
+
+constexpr int kChunkTokens = 128;
+
+// Header words at the start of the scratch buffer (device-written).
+enum PlanWord {
+  kPlanNumKvChunks = 0,   // chunks of K/V-cached requests
+  kPlanNumHidTiles = 1,   // chunks (M tiles) of hidden-cached requests
+  kPlanKvCounter = 2,     // dynamic work counter of the K/V kernel
+  kPlanHidCounter = 3,    // reserved
+  kPlanStatus = 4,        // non-zero when a kernel gave up on a bounded wait
+  kPlanWords = 64
+};
+
+struct WorkspaceLayout {
+  int batch, heads, head_size, max_chunks;  // max_chunks = batch * chunks per longest request
+  size_t off_plan, off_part_offset, off_kv_chunks, off_hid_tiles, off_ml, off_acc, total;
+};
+
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+inline WorkspaceLayout workspace_layout(int batch, int max_blocks_per_seq, int block_size,
+                                        int heads, int head_size) {
+  WorkspaceLayout w;
+  w.batch = batch; w.heads = heads; w.head_size = head_size;
+  const int64_t max_tokens = (int64_t)max_blocks_per_seq * block_size;
+  const int64_t per_req = (max_tokens + kChunkTokens - 1) / kChunkTokens;
+  const int64_t mc = (int64_t)batch * (per_req > 0 ? per_req : 1);
+  w.max_chunks = (int)mc;
+  size_t o = 0;
+  w.off_plan = o;        o = align_up(o + kPlanWords * sizeof(int), 256);
+  w.off_part_offset = o; o = align_up(o + (size_t)(batch + 1) * sizeof(int), 256);
+  w.off_kv_chunks = o;   o = align_up(o + (size_t)mc * sizeof(int2), 256);
+  w.off_hid_tiles = o;   o = align_up(o + (size_t)mc * sizeof(int2), 256);
+  w.off_ml = o;          o = align_up(o + (size_t)mc * heads * 2 * sizeof(float), 256);
+  w.off_acc = o;         o = align_up(o + (size_t)mc * heads * head_size * sizeof(float), 256);
+  w.total = o;
+  return w;
+}
+
+struct WorkspacePtrs {
+  int* plan;
+  int* part_offset;   // [batch + 1] first partial slot of each request
+  int2* kv_chunks;    // (request, chunk) of K/V-cached requests, request order
+  int2* hid_tiles;    // (request, chunk) of hidden-cached requests, request order
+  float* part_ml;     // [slot][head][2]
+  float* part_acc;    // [slot][head][head_size]
+};
+
+inline WorkspacePtrs workspace_ptrs(void* base, const WorkspaceLayout& w) {
+  char* b = static_cast<char*>(base);
+  WorkspacePtrs p;
+  p.plan = reinterpret_cast<int*>(b + w.off_plan);
+  p.part_offset = reinterpret_cast<int*>(b + w.off_part_offset);
+  p.kv_chunks = reinterpret_cast<int2*>(b + w.off_kv_chunks);
+  p.hid_tiles = reinterpret_cast<int2*>(b + w.off_hid_tiles);
+  p.part_ml = reinterpret_cast<float*>(b + w.off_ml);
+  p.part_acc = reinterpret_cast<float*>(b + w.off_acc);
+  return p;
+}
+
+struct AttnShape {
+  int batch, max_blocks_per_seq, heads, head_size, block_size;
+  int64_t query_stride, out_stride, block_stride;
+  float scale;
+  int dtype;
+};
+
+// cache_type may be NULL (all requests K/V-cached).
+int launch_plan(const WorkspacePtrs& ws, const int32_t* seq_lens, const int32_t* cache_type,
+                int batch, int max_blocks_per_seq, int block_size, cudaStream_t stream);
+
+int launch_kv_attention(const WorkspacePtrs& ws, const void* query, const void* key_cache,
+                        const void* value_cache, const int32_t* block_tables,
+                        const int32_t* seq_lens, const AttnShape& s, cudaStream_t stream);
+
+int launch_combine(const WorkspacePtrs& ws, void* out, const int32_t* seq_lens,
+                   const AttnShape& s, cudaStream_t stream);
+
+bool kv_attention_supported(int dtype, int head_size);
+
+// Argument checks shared by the attention entry points.
+int check_attention_args(const char* op, const void* out, const void* query, const void* key_cache,
+                         const void* value_cache, const int32_t* block_tables,
+                         const int32_t* seq_lens, const AttnShape& s, const void* workspace,
+                         size_t workspace_bytes, bool need_kv);
+
+}  // namespace aps

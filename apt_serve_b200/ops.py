@@ -1,0 +1,69 @@
+"""The three ``vllm._custom_ops`` entry points the reference's attention backend
+calls (additional_designs/attention/backends/aptserve_flash_attn.py:44-65,
+338-385), with vLLM 0.5.0's signatures."""
+from __future__ import annotations
+
+import ctypes
+from typing import List
+
+import torch
+
+from . import _native as N
+
+
+def reshape_and_cache_flash(key: torch.Tensor, value: torch.Tensor, key_cache: torch.Tensor,
+                            value_cache: torch.Tensor, slot_mapping: torch.Tensor,
+                            kv_cache_dtype: str = "auto") -> None:
+    """``key_cache[slot // BS, slot % BS] = key[t]`` (and value) for ``slot >= 0``.
+    ``key`` / ``value``: ``[T, H, D]``; caches ``[NB, BS, H, D]``."""
+    if kv_cache_dtype != "auto":  # aptserve_flash_attn.py:311-312: no FP8 cache here
+        raise ValueError(f"kv_cache_dtype {kv_cache_dtype!r} is not supported")
+    dev = N.require_cuda(key, value, key_cache, value_cache, slot_mapping)
+    if slot_mapping.dtype != torch.int64:
+        raise RuntimeError("slot_mapping must be int64")
+    if key.dtype != key_cache.dtype or value.dtype != value_cache.dtype or key.dtype != value.dtype:
+        raise RuntimeError("reshape_and_cache_flash: dtypes differ")
+    if key_cache.stride(0) != value_cache.stride(0):
+        raise RuntimeError("reshape_and_cache_flash: cache block strides differ")
+    if key.shape[0] > 0 and not (key[0].is_contiguous() and value[0].is_contiguous()):
+        raise RuntimeError("reshape_and_cache_flash: token rows must be contiguous")
+    with torch.cuda.device(dev):
+        N.check(N.lib().aps_reshape_and_cache(
+            N.ptr(key), N.ptr(value), N.ptr(key_cache), N.ptr(value_cache),
+            N.ptr(slot_mapping.contiguous()), slot_mapping.size(0), key.size(1), key.size(2),
+            key_cache.size(1), key.stride(0), value.stride(0), key_cache.stride(0),
+            N.dtype_enum(key), N.current_stream(dev)))
+
+
+def copy_blocks(key_caches: List[torch.Tensor], value_caches: List[torch.Tensor],
+                block_mapping: torch.Tensor) -> None:
+    """Copy-on-write block copies for every layer; ``block_mapping`` is an int64
+    ``[n, 2]`` device tensor of ``(src, dst)`` block numbers."""
+    if len(key_caches) != len(value_caches):
+        raise RuntimeError("copy_blocks: key / value cache lists differ in length")
+    if not key_caches or block_mapping.numel() == 0:
+        return
+    dev = N.require_cuda(block_mapping, *key_caches, *value_caches)
+    if block_mapping.dtype != torch.int64:
+        raise RuntimeError("copy_blocks: block_mapping must be int64")
+    first = key_caches[0]
+    block_bytes = first.stride(0) * first.element_size()
+    for t in list(key_caches) + list(value_caches):
+        if t.stride(0) * t.element_size() != block_bytes or not t[0].is_contiguous():
+            raise RuntimeError("copy_blocks: every cache must have the same contiguous block layout")
+    n = len(key_caches)
+    karr = (ctypes.c_void_p * n)(*[t.data_ptr() for t in key_caches])
+    varr = (ctypes.c_void_p * n)(*[t.data_ptr() for t in value_caches])
+    with torch.cuda.device(dev):
+        N.check(N.lib().aps_copy_blocks(karr, varr, n, N.ptr(block_mapping.contiguous()),
+                                        block_mapping.size(0), block_bytes,
+                                        N.current_stream(dev)))
+
+
+def swap_blocks(src: torch.Tensor, dst: torch.Tensor, src_to_dst: torch.Tensor) -> None:
+    """GPU <-> pinned-CPU block moves (aptserve_flash_attn.py:44-56).  PCIe-bound
+    memcpy glue, outside the rewritten kernels: one async copy per pair on the
+    current stream, like the third-party op it stands in for."""
+    pairs = src_to_dst.tolist()
+    for s, d in pairs:
+        dst[d].copy_(src[s], non_blocking=True)

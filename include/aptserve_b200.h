@@ -1,0 +1,222 @@
+/*
+ * aptserve_b200.h -- C ABI of the B200 (sm_100a) hybrid-cache data path.
+ *
+ * Every entry point replaces one operator the Apt-Serve reference reaches from
+ * Python on its decode / cache-write hot path.  File:line citations name the
+ * reference interface each one stands in for (paths inside the reference
+ * project, under additional_designs/):
+ *   mc.cu  = mixed_cache_kernels/mixed_cache.cu
+ *   fa.py  = attention/backends/aptserve_flash_attn.py
+ *   opt.py = model_executor/models/aptserve_opt.py
+ *   lin.py = model_executor/layers/aptserve_linear.py
+ *
+ * Conventions
+ *  - plain pointers and sizes only; all data pointers are DEVICE pointers unless
+ *    a parameter says "host";
+ *  - strides are in ELEMENTS of the payload dtype;
+ *  - index tensors are int64 (slot mappings, index lists) or int32 (block tables,
+ *    sequence lengths), exactly as the reference's model runner builds them;
+ *  - every call enqueues on `stream` (a cudaStream_t passed as void*) of the
+ *    CURRENT device and returns without synchronising;
+ *  - nothing is allocated or freed for the caller and no pointer is retained
+ *    after return, except the per-device objects created by aps_* on first use
+ *    (an auxiliary stream, two events) which live until process exit;
+ *  - the return value is an aps_status; no C++ exception crosses the boundary;
+ *    aps_last_error() gives a human-readable message for the calling thread.
+ */
+#ifndef APTSERVE_B200_H_
+#define APTSERVE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum aps_status {
+  APS_OK = 0,
+  APS_ERR_NULL_POINTER = 1,  /* a required pointer is NULL                        */
+  APS_ERR_MISALIGNED = 2,    /* pointer / stride not aligned as the op requires    */
+  APS_ERR_DTYPE = 3,         /* dtype enum not supported by this op                */
+  APS_ERR_SHAPE = 4,         /* negative / inconsistent sizes or strides           */
+  APS_ERR_UNSUPPORTED = 5,   /* head size / block size / hidden size not supported */
+  APS_ERR_WORKSPACE = 6,     /* workspace NULL, misaligned or too small            */
+  APS_ERR_CUDA = 7,          /* a CUDA runtime / driver call failed                */
+  APS_ERR_DEVICE = 8         /* device-side status word reported a failure         */
+} aps_status;
+
+typedef enum aps_dtype {
+  APS_F32 = 0,
+  APS_F16 = 1,
+  APS_BF16 = 2
+} aps_dtype;
+
+/* Message describing the last non-zero status returned on this thread. */
+const char* aps_last_error(void);
+
+/* Library version string, e.g. "aptserve_b200 0.1 (sm_100a)". */
+const char* aps_version(void);
+
+/* ------------------------------------------------------------------------ */
+/* Paged cache writes (bit-exact data movement, HBM-bound)                   */
+/* ------------------------------------------------------------------------ */
+
+/*
+ * Replaces vllm._custom_ops.reshape_and_cache_flash as called at fa.py:338-345,
+ * fa.py:348-355 and fa.py:378-385:
+ *   key_cache[slot / BS, slot % BS, :, :] = key[t]   (same for value), slot < 0 skipped.
+ * key/value: [T, H, D] with row strides key_stride / value_stride;
+ * caches: [NB, BS, H, D], block stride block_stride, [BS, H, D] contiguous inside.
+ */
+int aps_reshape_and_cache(const void* key, const void* value, void* key_cache,
+                          void* value_cache, const int64_t* slot_mapping,
+                          int64_t num_tokens, int num_heads, int head_size,
+                          int block_size, int64_t key_stride, int64_t value_stride,
+                          int64_t block_stride, int dtype, void* stream);
+
+/*
+ * Replaces mixed_cache_ops.hidden_to_cache (mc.cu:119-147, kernel mc.cu:31-53;
+ * called at opt.py:108-109): for i in [0, n):
+ *   slot = slot_mapping[target_slot_idx[i]]; if slot >= 0:
+ *   paged_cache[slot * slot_stride + (0..hidden_size)] = hidden[src_idx[i], :]
+ * slot_stride is paged_cache.stride(2) of the [2, NB, BS, H, D] tensor.
+ */
+int aps_hidden_to_cache(const void* hidden, void* paged_cache,
+                        const int64_t* slot_mapping, const int64_t* src_idx,
+                        const int64_t* target_slot_idx, int64_t n, int hidden_size,
+                        int64_t hidden_stride, int64_t slot_stride, int dtype,
+                        void* stream);
+
+/*
+ * Replaces mixed_cache_ops.cache_to_hidden (mc.cu:150-176, kernel mc.cu:6-28;
+ * called at opt.py:120-121): for i in [0, n): t = dst_idx[i];
+ *   slot = slot_mapping[t]; if slot >= 0: hidden[t, :] = paged_cache[slot * slot_stride + ...]
+ */
+int aps_cache_to_hidden(void* hidden, const void* paged_cache,
+                        const int64_t* slot_mapping, const int64_t* dst_idx, int64_t n,
+                        int hidden_size, int64_t hidden_stride, int64_t slot_stride,
+                        int dtype, void* stream);
+
+/*
+ * Replaces mixed_cache_ops.mixed_kv_to_cache (mc.cu:179-230, kernel mc.cu:56-116;
+ * called at fa.py:363-373):
+ *   b in [0, n_kv):  tok = kv_cache_use_tot[b], slot = slot_mapping[tok]:
+ *                    key/value[tok] -> k_cache/v_cache AND shared_k/shared_v at slot
+ *   j in [0, n_hidden): tok = hidden_cache_use_tot[j], slot = slot_mapping_shared[j]:
+ *                    key/value[tok] -> shared_k/shared_v at slot
+ * (j is the hidden token's ordinal; the reference's `blockIdx.x % (2*n_kv)` at
+ * mc.cu:88 equals it only while n_hidden <= 2*n_kv.)
+ */
+int aps_mixed_kv_to_cache(const void* key, const void* value, void* k_cache,
+                          void* v_cache, void* shared_k_cache, void* shared_v_cache,
+                          const int64_t* slot_mapping,
+                          const int64_t* slot_mapping_shared,
+                          const int64_t* kv_cache_use_tot,
+                          const int64_t* hidden_cache_use_tot, int64_t n_kv,
+                          int64_t n_hidden, int num_heads, int head_size,
+                          int block_size, int64_t key_stride, int64_t value_stride,
+                          int64_t block_stride, int64_t shared_block_stride, int dtype,
+                          void* stream);
+
+/*
+ * Replaces vllm._custom_ops.copy_blocks as called at fa.py:58-65:
+ * for every layer l and every row (src, dst) of block_mapping [num_pairs, 2]:
+ *   key_caches[l][dst] = key_caches[l][src]; value_caches[l][dst] = value_caches[l][src].
+ * key_cache_ptrs / value_cache_ptrs are HOST arrays of num_layers device
+ * pointers; block_bytes is the size of one block of one plane.
+ */
+int aps_copy_blocks(void* const* key_cache_ptrs, void* const* value_cache_ptrs,
+                    int num_layers, const int64_t* block_mapping, int64_t num_pairs,
+                    int64_t block_bytes, void* stream);
+
+/* ------------------------------------------------------------------------ */
+/* Decode attention                                                          */
+/* ------------------------------------------------------------------------ */
+
+/*
+ * Bytes of scratch the two attention calls below need for a batch of `batch`
+ * requests whose block tables are `max_blocks_per_seq` wide.  The caller
+ * allocates it (256-byte aligned) and may reuse it across calls on one stream.
+ */
+size_t aps_attention_workspace_bytes(int batch, int max_blocks_per_seq,
+                                     int block_size, int num_heads, int head_size);
+
+/*
+ * Replaces vllm_flash_attn.flash_attn_with_kvcache as called at fa.py:452-461
+ * (decode batch, all requests K/V-cached):
+ *   out[r, h, :] = softmax(scale * q[r, h] . K_r[:, h]) @ V_r[:, h]
+ * over the first seq_lens[r] tokens found through block_tables[r].
+ * query/out: [B, H*D] with row strides; caches [NB, BS, H, D];
+ * block_tables int32 [B, max_blocks_per_seq]; seq_lens int32 [B].
+ */
+int aps_paged_decode_attention(void* out, const void* query, const void* key_cache,
+                               const void* value_cache, const int32_t* block_tables,
+                               const int32_t* seq_lens, int batch,
+                               int max_blocks_per_seq, int num_heads, int head_size,
+                               int block_size, int64_t query_stride,
+                               int64_t out_stride, int64_t block_stride, float scale,
+                               void* workspace, size_t workspace_bytes, int dtype,
+                               void* stream);
+
+/*
+ * Hybrid decode attention: one call for the decode branch of
+ * OPTAttention.forward with hidden-cached requests (opt.py:111-124: gather of
+ * cached hidden rows, K/V re-projection lin.py:123-130) followed by the cache
+ * write + paged attention of fa.py:356-387 and fa.py:462-473 -- without the
+ * hidden_holder buffer, the [N_tot, 2HD] K/V tensor or the shared cache.
+ *
+ *   cache_type[r] == 0: K/V rows come from key_cache/value_cache through
+ *                       block_tables[r] (as aps_paged_decode_attention);
+ *   cache_type[r] != 0: hidden rows X_r come from the flat rows of hidden_cache
+ *                       (row id = block_tables[r][t / BS] * BS + t % BS, row
+ *                       stride hidden_row_stride, first hidden_size elements);
+ *                       K = X_r W_k^T + b_k, V = X_r W_v^T + b_v on the tensor
+ *                       cores, fp32 accumulation, then the same softmax.
+ * w_k / w_v: [H*D, hidden_size] row-major with row stride w_stride (the K and V
+ * thirds of the fused QKV weight, lin.py:123-125); b_k / b_v: [H*D] or NULL.
+ * num_hidden_rows is the number of addressable rows of hidden_cache
+ * (2*NB*BS for the reference layout).  fp16 / bf16 with head_size 128 use the
+ * tcgen05 path; other supported combinations use a CUDA-core re-projection.
+ */
+int aps_hybrid_decode_attention(void* out, const void* query, const void* key_cache,
+                                const void* value_cache, const void* hidden_cache,
+                                const void* w_k, const void* b_k, const void* w_v,
+                                const void* b_v, const int32_t* block_tables,
+                                const int32_t* seq_lens, const int32_t* cache_type,
+                                int batch, int max_blocks_per_seq, int num_heads,
+                                int head_size, int hidden_size, int block_size,
+                                int64_t query_stride, int64_t out_stride,
+                                int64_t block_stride, int64_t hidden_row_stride,
+                                int64_t num_hidden_rows, int64_t w_stride, float scale,
+                                void* workspace, size_t workspace_bytes, int dtype,
+                                void* stream);
+
+/*
+ * The K/V re-projection on its own (opt.py:123 -> lin.py:123-130):
+ *   kv[t, 0:HD] = X[t] W_k^T + b_k ; kv[t, HD:2HD] = X[t] W_v^T + b_v ,  t in [0, n_rows)
+ * Same tensor-core main loop as the hybrid attention; fp16 / bf16, head_size 128.
+ *   block_ids == NULL : X[t] is row t of x (the dense hidden_holder of opt.py:112-121);
+ *   block_ids != NULL : X[t] is row block_ids[t / 16] * 16 + t % 16 of x, i.e. x is a
+ *                       paged hidden cache read in 16-row blocks (int32 ids).
+ * x: rows of x_row_stride elements, num_x_rows addressable rows; kv: [n_rows, 2*HD]
+ * with row stride kv_stride.  status_word (device int, zeroed by the caller, may be
+ * NULL) receives a non-zero code if a bounded device-side wait ran out.
+ */
+int aps_kv_reprojection(void* kv, const void* x, const int32_t* block_ids, int64_t n_rows,
+                        const void* w_k, const void* b_k, const void* w_v, const void* b_v,
+                        int num_heads, int head_size, int hidden_size, int64_t x_row_stride,
+                        int64_t num_x_rows, int64_t w_stride, int64_t kv_stride, int dtype,
+                        int* status_word, void* stream);
+
+/*
+ * Reads the status word the attention kernels keep in `workspace` (0 = fine,
+ * non-zero = a bounded device-side wait ran out in the last call that used this
+ * workspace).  Synchronises `stream`.  Meant for tests and debugging.
+ */
+int aps_attention_status(const void* workspace, int* host_status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* APTSERVE_B200_H_ */
