@@ -48,6 +48,7 @@ PROTOTYPES = {
     "aps_kv_reprojection": (c_int, [c_void_p] * 3 + [c_int64] + [c_void_p] * 4 + [c_int] * 3 +
                             [c_int64] * 4 + [c_int, c_void_p, c_void_p]),
     "aps_attention_status": (c_int, [c_void_p, c_void_p, c_void_p]),
+    "aps_set_profile_events": (c_int, [c_int, c_void_p, c_void_p]),
 }
 
 _lib = None

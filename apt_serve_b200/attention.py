@@ -160,8 +160,9 @@ def kv_reprojection(x: torch.Tensor, w_k: torch.Tensor, b_k: Optional[torch.Tens
                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``kv = [X W_k^T + b_k | X W_v^T + b_v]`` on the tensor cores (the
     ``kv_only`` projection of aptserve_linear.py:123-130).  ``x`` is a dense
-    ``[N, E]`` matrix, or -- with ``block_ids`` (int32) -- any tensor whose flat
-    rows of ``x.stride(-2)`` elements are read in 16-row blocks."""
+    ``[N, E]`` matrix, or -- with ``block_ids`` (int32) -- a paged cache
+    ``[2, NB, BS, H, D]`` whose flat rows of ``stride(2)`` elements are read in
+    16-row blocks."""
     dev = N.require_cuda(x, w_k, b_k, w_v, b_v, block_ids)
     hd, e = w_k.shape
     if block_ids is None:
@@ -170,7 +171,7 @@ def kv_reprojection(x: torch.Tensor, w_k: torch.Tensor, b_k: Optional[torch.Tens
         rows_total, row_stride = x.shape[0], x.stride(0)
         n = rows_total if n_rows is None else n_rows
     else:
-        row_stride = x.stride(-2)
+        row_stride = x.stride(2) if x.dim() == 5 else x.stride(-2)
         rows_total = x.numel() // row_stride
         n = block_ids.numel() * 16 if n_rows is None else n_rows
         block_ids = _i32(block_ids, "block_ids")

@@ -56,6 +56,19 @@ inline bool aligned_to(const void* p, size_t a) { return (reinterpret_cast<uintp
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
+// Optional timing hooks (see aps_set_profile_events): events recorded around the
+// K/V streaming kernel (which = 0) and the re-projection kernel (which = 1).
+struct ProfileEvents { cudaEvent_t start, stop; };
+ProfileEvents* profile_events(int which);
+
+struct ScopedProfile {
+  ProfileEvents* ev; cudaStream_t stream;
+  ScopedProfile(int which, cudaStream_t s) : ev(profile_events(which)), stream(s) {
+    if (ev->start) cudaEventRecord(ev->start, stream);
+  }
+  ~ScopedProfile() { if (ev->stop) cudaEventRecord(ev->stop, stream); }
+};
+
 // ---- device helpers ----------------------------------------------------------
 template <typename T> struct Elem;
 template <> struct Elem<float> {

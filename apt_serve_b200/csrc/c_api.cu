@@ -22,7 +22,20 @@ int sm_count() {
   return cached[dev];
 }
 
+ProfileEvents* profile_events(int which) {
+  static thread_local ProfileEvents ev[2] = {{nullptr, nullptr}, {nullptr, nullptr}};
+  return &ev[which & 1];
+}
+
 }  // namespace aps
+
+extern "C" int aps_set_profile_events(int which, void* start_event, void* stop_event) {
+  if (which < 0 || which > 1) return aps::fail(APS_ERR_SHAPE, "set_profile_events: which must be 0 or 1");
+  aps::ProfileEvents* ev = aps::profile_events(which);
+  ev->start = static_cast<cudaEvent_t>(start_event);
+  ev->stop = static_cast<cudaEvent_t>(stop_event);
+  return APS_OK;
+}
 
 extern "C" const char* aps_last_error(void) { return aps::last_error_buffer(); }
 

@@ -514,7 +514,10 @@ int launch_hidden(const CUtensorMap& mx, const CUtensorMap& mk, const CUtensorMa
                                   (int)kSmemBytes));
     configured[dev] = true;
   }
-  hidden_path_kernel<T, MODE><<<sm_count(), kThreads, kSmemBytes, stream>>>(mx, mk, mv, p);
+  {
+    ScopedProfile prof(1, stream);
+    hidden_path_kernel<T, MODE><<<sm_count(), kThreads, kSmemBytes, stream>>>(mx, mk, mv, p);
+  }
   return launch_status("hidden_path_kernel");
 }
 

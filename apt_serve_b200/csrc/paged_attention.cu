@@ -240,6 +240,7 @@ int launch_kv_typed(const WorkspacePtrs& ws, const void* query, const void* key_
                     const AttnShape& s, cudaStream_t stream) {
   const int grid = sm_count() * 2;
   const float scale_log2 = s.scale * 1.4426950408889634f;
+  ScopedProfile prof(0, stream);
   kv_attention_kernel<T, D><<<grid, kKvWarps * 32, 0, stream>>>(
       ws.plan, ws.part_offset, ws.kv_chunks, ws.part_ml, ws.part_acc, (const T*)query,
       (const T*)key_cache, (const T*)value_cache, block_tables, seq_lens, s.max_blocks_per_seq,

@@ -216,19 +216,16 @@ def make_decode_workload(shape: LayerShape, seq_lens: Sequence[int], use_hidden:
 
     kv_std = 0.02 * math.sqrt(e)
     alias = hd_rank == e
-    if tp_size == 1:
-        kv_cache = randn(2, nb, bs, h_rank, d, std=kv_std)
-    else:
-        full = None
-        # draw per plane and block slab at full width, keep this rank's heads
-        kv_cache = torch.empty(2, nb, bs, h_rank, d, dtype=shape.dtype, device=dev)
-        slab = max(1, (1 << 26) // (bs * hd_full))
-        for p in range(2):
-            for i in range(0, nb, slab):
-                n = min(slab, nb - i)
-                full = randn(n, bs, shape.num_heads, d, std=kv_std)
-                kv_cache[p, i:i + n] = full[:, :, tp_rank * h_rank:(tp_rank + 1) * h_rank]
-        del full
+    # K/V planes: drawn per plane and per slab of blocks at FULL width, then cut to this
+    # rank's heads, so that every tensor-parallel size sees the same numbers
+    kv_cache = torch.empty(2, nb, bs, h_rank, d, dtype=shape.dtype, device=dev)
+    slab = max(1, (1 << 26) // (bs * hd_full))
+    for p in range(2):
+        for i in range(0, nb, slab):
+            n = min(slab, nb - i)
+            full = randn(n, bs, shape.num_heads, d, std=kv_std)
+            kv_cache[p, i:i + n] = full[:, :, tp_rank * h_rank:(tp_rank + 1) * h_rank]
+            del full
     if alias:
         hidden_cache = kv_cache
     else:

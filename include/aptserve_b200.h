@@ -216,6 +216,16 @@ int aps_kv_reprojection(void* kv, const void* x, const int32_t* block_ids, int64
  */
 int aps_attention_status(const void* workspace, int* host_status, void* stream);
 
+/*
+ * Timing hook for benchmarks (no counterpart in the reference, whose kernels are
+ * timed with commented-out torch.cuda.synchronize() calls, fa.py:374-387):
+ * while set, the attention calls of THIS THREAD record `start_event` just before
+ * and `stop_event` just after the launch of the K/V streaming kernel (which = 0)
+ * or of the re-projection kernel (which = 1), on the stream of the call.  Events
+ * are cudaEvent_t handles owned by the caller; pass NULL, NULL to switch off.
+ */
+int aps_set_profile_events(int which, void* start_event, void* stop_event);
+
 #ifdef __cplusplus
 }
 #endif
