@@ -1,0 +1,428 @@
+#!/usr/bin/env python
+"""Benchmark of the hybrid-cache decode layer-step.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config C]
+
+One step = the new token's cache write for every request (K/V rows for K/V-cached
+requests, the layer-input row for hidden-cached ones) followed by hybrid decode
+attention over the whole ragged batch.  With N > 1 the attention heads and the
+matching W_k / W_v / W_o slices are sharded over the N ranks (hidden cache
+replicated) and the step also holds the o_proj GEMM and its all-reduce.
+
+N = 1 runs configuration 2 (OPT-13B layer, fp16, 256 requests, lognormal context
+lengths, half of them hidden-cached).  Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+METRIC = "hybrid-cache decode tokens/s @OPT-13B layer, B=256"
+UNIT = "tokens/s"
+
+
+# --------------------------------------------------------------------------- #
+# helpers
+# --------------------------------------------------------------------------- #
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "tflops_burst": float(p["bf16_tflops"]),
+                "tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
+                "source": "measured"}
+    except Exception:
+        return {"hbm_gbs": 6650.0, "tflops_burst": 1590.0, "tflops_sustained": 1400.0,
+                "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100", "-i", str(self.gpu_index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2])); power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm), "power_w_max": max(power) if power else None}
+
+
+def dist_env():
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), \
+        int(os.environ.get("WORLD_SIZE", 1))
+
+
+def cpu_sample_requests(lens, hid, flop_budget, e, hd):
+    """A bounded sample of the batch for the host-core baseline: hidden requests in
+    batch order until their re-projection reaches ``flop_budget`` FLOPs, and as many
+    K/V requests, which keeps the configuration's cache-type mix."""
+    picked_h, flops = [], 0.0
+    for r, (s, h) in enumerate(zip(lens, hid)):
+        if h:
+            picked_h.append(r)
+            flops += 2.0 * s * e * 2 * hd
+            if flops >= flop_budget:
+                break
+    n_h_total = sum(1 for h in hid if h)
+    n_kv_total = len(hid) - n_h_total
+    want_kv = len(picked_h) if n_h_total == 0 else round(len(picked_h) * n_kv_total / max(1, n_h_total))
+    if not picked_h:
+        want_kv = min(n_kv_total, 32)
+    picked_kv = [r for r, h in enumerate(hid) if not h][:want_kv]
+    return sorted(picked_h + picked_kv)
+
+
+def run_cpu_port(workload_cpu, requests, steps, warmup):
+    """The oracle's layer-step (cache writes + hybrid decode attention, fp32) on the host
+    cores for the sampled requests; returns seconds per step."""
+    from oracle import hybrid_cache_oracle as O
+    w = workload_cpu
+    wk, bk, wv, bv = w.kv_weights()
+    wk, wv = wk.float(), wv.float()
+    bk, bv = bk.float(), bv.float()
+
+    def one():
+        return O.decode_layer_step(w.hidden_states, w.query, w.new_key, w.new_value, w.kv_cache,
+                                   w.hidden_cache, wk, bk, wv, bv, w.meta, w.scale,
+                                   requests=requests)
+    for _ in range(warmup):
+        one()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        one()
+    return (time.perf_counter() - t0) / max(1, steps)
+
+
+# --------------------------------------------------------------------------- #
+# the step
+# --------------------------------------------------------------------------- #
+class LayerStep:
+    """Holds one rank's tensors and runs the measured step through the package's public API."""
+
+    def __init__(self, w, tp_group=None):
+        from apt_serve_b200 import attention as A
+        self.A = A
+        self.w = w
+        self.tp_group = tp_group
+        m = w.meta
+        h, d = w.heads, w.shape.head_dim
+        self.h, self.d = h, d
+        self.wk, self.bk, self.wv, self.bv = w.kv_weights()
+        self.kv_rows = m.kv_request_rows
+        self.kv_slots = m.slot_mapping[m.kv_cache_use_tot].contiguous()
+        # per-request slot of the new token: K/V requests write K/V rows, hidden requests
+        # write their layer-input row; the other kind is masked with -1 (skipped)
+        new_slot = m.slot_mapping[m.hidden_holder_upd]
+        self.kv_new_slots = torch.where(m.cache_type != 0, torch.full_like(new_slot, -1), new_slot)
+        self.out = torch.empty_like(w.query)
+        self.workspace = A.attention_workspace(w.query.device, w.query.shape[0],
+                                               m.private_block_tables.shape[1], w.shape.block_size, h, d)
+
+    def cache_writes(self, hidden_states, new_key, new_value, kv_new_slots):
+        from apt_serve_b200 import mixed_cache_ops, ops
+        w, m = self.w, self.w.meta
+        ops.reshape_and_cache_flash(new_key.view(-1, self.h, self.d), new_value.view(-1, self.h, self.d),
+                                    w.kv_cache[0], w.kv_cache[1], kv_new_slots, "auto")
+        mixed_cache_ops.hidden_to_cache(hidden_states, w.hidden_cache, m.slot_mapping,
+                                        m.hidden_cache_use_input, m.hidden_cache_store_tot)
+
+    def attention(self, query, tables, seq_lens, cache_type):
+        return self.A.hybrid_decode_attention(query, self.w.kv_cache, self.w.hidden_cache, self.wk,
+                                              self.bk, self.wv, self.bv, tables, seq_lens, cache_type,
+                                              self.w.scale, out=self.out, workspace=self.workspace)
+
+    def o_proj(self, attn_out):
+        import torch.distributed as dist
+        y = torch.nn.functional.linear(attn_out, self.w.o_weight)
+        dist.all_reduce(y, group=self.tp_group)
+        return y + self.w.o_bias
+
+    def step(self):
+        w, m = self.w, self.w.meta
+        self.cache_writes(w.hidden_states, w.new_key, w.new_value, self.kv_new_slots)
+        out = self.attention(w.query, m.private_block_tables, m.seq_lens_tensor, m.cache_type)
+        if self.tp_group is not None:
+            out = self.o_proj(out)
+        return out
+
+
+# --------------------------------------------------------------------------- #
+# arms
+# --------------------------------------------------------------------------- #
+def run_ours(args):
+    import ctypes
+    from apt_serve_b200 import _native as N
+    from apt_serve_b200.workloads import (CONFIG_SHAPES, algorithmic_work, draw_decode_batch,
+                                          make_decode_workload)
+    rank, local_rank, world = dist_env()
+    n_gpus = args.gpus
+    assert world == n_gpus or world == 1, f"WORLD_SIZE {world} does not match --gpus {n_gpus}"
+    tp = world
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    group = None
+    if tp > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD
+
+    cfg = args.config
+    shape = CONFIG_SHAPES[cfg]
+    seed = 1000 + cfg
+    lens, hid = draw_decode_batch(cfg, seed, batch=args.batch, hidden_fraction=args.hidden_fraction)
+    w = make_decode_workload(shape, lens, hid, seed, dev, tp_rank=rank, tp_size=tp)
+    work = algorithmic_work(shape, lens, hid, tp)
+    B = len(lens)
+    st = LayerStep(w, group)
+    peaks = measured_peaks()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if tp > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing: warm-up, then exactly K steps ----
+    for _ in range(max(args.warmup, 3)):
+        st.step()
+    barrier()
+    K = args.steps
+    ev_kv = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+    ev_hid = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+    for a, b in ev_kv + ev_hid:   # create the underlying handles
+        a.record(); b.record()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    lib = N.lib()
+    e0.record()
+    for i in range(K):
+        lib.aps_set_profile_events(0, ctypes.c_void_p(ev_kv[i][0].cuda_event), ctypes.c_void_p(ev_kv[i][1].cuda_event))
+        lib.aps_set_profile_events(1, ctypes.c_void_p(ev_hid[i][0].cuda_event), ctypes.c_void_p(ev_hid[i][1].cuda_event))
+        st.step()
+    e1.record()
+    barrier()
+    lib.aps_set_profile_events(0, None, None)
+    lib.aps_set_profile_events(1, None, None)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_total = e0.elapsed_time(e1)
+    t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
+    if tp > 1:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    ms_per_step = float(t.item()) / K
+    kv_ms = statistics.mean(a.elapsed_time(b) for a, b in ev_kv)
+    hid_ms = statistics.mean(a.elapsed_time(b) for a, b in ev_hid)
+    status = st.A.attention_status(st.workspace)
+
+    # ---- end to end through the public API with host buffers ----
+    m = w.meta
+    host_in = {
+        "hidden_states": w.hidden_states.cpu().pin_memory(), "query": w.query.cpu().pin_memory(),
+        "new_key": w.new_key.cpu().pin_memory(), "new_value": w.new_value.cpu().pin_memory(),
+        "tables": m.private_block_tables.cpu().pin_memory(), "seq_lens": m.seq_lens_tensor.cpu().pin_memory(),
+        "cache_type": m.cache_type.cpu().pin_memory(), "kv_new_slots": st.kv_new_slots.cpu().pin_memory(),
+    }
+    dev_in = {k: torch.empty_like(v, device=dev) for k, v in host_in.items()}
+    out_shape = (B, shape.hidden) if tp > 1 else tuple(w.query.shape)
+    host_out = torch.empty(out_shape, dtype=shape.dtype).pin_memory()
+    h2d = sum(v.numel() * v.element_size() for v in host_in.values())
+    d2h = host_out.numel() * host_out.element_size()
+
+    def e2e_step():
+        for k, v in host_in.items():
+            dev_in[k].copy_(v, non_blocking=True)
+        st.cache_writes(dev_in["hidden_states"], dev_in["new_key"], dev_in["new_value"], dev_in["kv_new_slots"])
+        out = st.attention(dev_in["query"], dev_in["tables"], dev_in["seq_lens"], dev_in["cache_type"])
+        if tp > 1:
+            out = st.o_proj(out)
+        host_out.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(K):
+        e2e_step()
+    barrier()
+    e2e_s = (time.perf_counter() - t0) / K
+    t = torch.tensor([e2e_s], device=dev, dtype=torch.float64)
+    if tp > 1:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    e2e_s = float(t.item())
+
+    if rank != 0:
+        if tp > 1:
+            torch.distributed.destroy_process_group()
+        return
+
+    tflops = work["reprojection_flops"] / (hid_ms * 1e-3) / 1e12 if hid_ms > 0 and work["t_hidden"] else 0.0
+    kv_gbs = work["kv_attention_bytes"] / (kv_ms * 1e-3) / 1e9 if kv_ms > 0 and work["t_kv"] else 0.0
+    if work["t_hidden"] > 0:
+        roofline = {"kernel": "hidden_path_kernel (tcgen05 re-projection + softmax partials)",
+                    "bound": "tensor", "achieved": round(tflops, 2), "peak": peaks["tflops_sustained"],
+                    "unit": "TFLOP/s", "frac": round(tflops / peaks["tflops_sustained"], 4),
+                    "frac_of_burst_peak": round(tflops / peaks["tflops_burst"], 4),
+                    "peak_source": peaks["source"] + " (sustained bf16 figure: the kernel runs inside a long step)",
+                    "ms_per_launch": round(hid_ms, 4), "flops_per_launch": work["reprojection_flops"],
+                    "traffic": None}
+    else:
+        roofline = {"kernel": "kv_attention_kernel", "bound": "hbm", "achieved": round(kv_gbs, 1),
+                    "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(kv_gbs / peaks["hbm_gbs"], 4),
+                    "peak_source": peaks["source"], "ms_per_launch": round(kv_ms, 4),
+                    "bytes_per_launch": work["kv_attention_bytes"], "traffic": None}
+    roofline_kv = {"kernel": "kv_attention_kernel (K/V streaming)", "bound": "hbm",
+                   "achieved": round(kv_gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                   "frac": round(kv_gbs / peaks["hbm_gbs"], 4), "ms_per_launch": round(kv_ms, 4),
+                   "bytes_per_launch": work["kv_attention_bytes"]}
+
+    # ---- host-core baseline on a bounded sample (rank 0, N = 1 only) ----
+    cpu_baseline = None
+    if tp == 1 and not args.no_cpu_baseline:
+        hd = w.heads * shape.head_dim
+        sample = cpu_sample_requests(lens, hid, args.cpu_flops, shape.hidden, hd)
+        cpu_w = w.cpu()
+        sec = run_cpu_port(cpu_w, sample, 1, 0)
+        cpu_baseline = {"value": round(len(sample) / sec, 3), "unit": UNIT, "cores": torch.get_num_threads(),
+                        "host_cpus": os.cpu_count(), "kind": "port",
+                        "sample": f"{len(sample)} of {B} requests in batch order keeping the hidden/K-V mix "
+                                  f"({sum(lens[r] for r in sample)} cached tokens), one step, "
+                                  f"{sec:.2f} s; tokens/s = sampled requests / time"}
+        del cpu_w
+
+    line = {
+        "metric": METRIC, "value": round(B / (ms_per_step * 1e-3), 2), "unit": UNIT, "n_gpus": n_gpus,
+        "steps": K, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4),
+        "higher_is_better": True, "scaling": "strong" if tp > 1 else "weak", "vs_baseline": None,
+        "dtype": {torch.float16: "f16", torch.bfloat16: "bf16", torch.float32: "f32"}[shape.dtype],
+        "data": "synthetic",
+        "config": {"workload": f"config {cfg}: {shape.name} layer ({shape.num_heads} heads x {shape.head_dim}, "
+                               f"hidden {shape.hidden}), {B} decode requests, {sum(hid)} hidden-cached, "
+                               f"T_kv={work['t_kv']} T_hidden={work['t_hidden']} cached tokens per rank view",
+                   "step": "new-token cache writes + hybrid decode attention" + (" + o_proj + all-reduce" if tp > 1 else ""),
+                   "parallelism": f"tp{tp}" if tp > 1 else "single GPU",
+                   "l2": f"inputs larger than L2: {(work['kv_attention_bytes'] + work['hidden_bytes']) / 1e9:.2f} GB streamed per step",
+                   "seed": seed},
+        "clocks": clocks,
+        "e2e": {"value": round(B / e2e_s, 2), "unit": UNIT, "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_s * 1e3, 4)},
+        "gpu_launches": 6 * K,
+        "roofline": roofline, "roofline_kv_path": roofline_kv,
+        "device_status": status,
+    }
+    if cpu_baseline is not None:
+        line["cpu_baseline"] = cpu_baseline
+    print(json.dumps(line))
+    if tp > 1:
+        torch.distributed.destroy_process_group()
+
+
+def run_reference(args):
+    """The reference path's semantics on the host cores (the oracle port: the reference
+    itself needs vLLM 0.5.0.post1 and a GPU), on a bounded sample of the same workload."""
+    rank, _, world = dist_env()
+    if rank != 0:
+        return
+    from apt_serve_b200.workloads import CONFIG_SHAPES, draw_decode_batch, make_decode_workload
+    cfg = args.config
+    shape = CONFIG_SHAPES[cfg]
+    seed = 1000 + cfg
+    lens, hid = draw_decode_batch(cfg, seed, batch=args.batch, hidden_fraction=args.hidden_fraction)
+    hd = shape.num_heads * shape.head_dim
+    sample = cpu_sample_requests(lens, hid, args.cpu_flops, shape.hidden, hd)
+    # only the sampled requests are materialised on the host (same distributions, same seed)
+    s_lens = [lens[r] for r in sample]
+    s_hid = [hid[r] for r in sample]
+    w = make_decode_workload(shape, s_lens, s_hid, seed, "cpu")
+    reqs = list(range(len(sample)))
+    sec = run_cpu_port(w, reqs, args.steps, min(args.warmup, 1))
+    value = len(sample) / sec
+    desc = (f"{len(sample)} of {len(lens)} requests of config {cfg} keeping the hidden/K-V mix "
+            f"({sum(s_lens)} cached tokens) per step; tokens/s = sampled requests / time")
+    line = {"impl": "reference", "metric": METRIC, "value": round(value, 3), "unit": UNIT,
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": min(args.warmup, 1),
+            "ms_per_step": round(sec * 1e3, 3), "higher_is_better": True,
+            "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": f"config {cfg}: {shape.name} layer, bounded sample", "seed": seed},
+            "cpu_baseline": {"value": round(value, 3), "unit": UNIT, "cores": torch.get_num_threads(),
+                             "host_cpus": os.cpu_count(), "kind": "port", "sample": desc},
+            "e2e": {"value": round(value, 3), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4, 5])
+    ap.add_argument("--hidden-fraction", type=float, default=None)
+    ap.add_argument("--batch", type=int, default=None, help="override the configuration's request count")
+    ap.add_argument("--cpu-flops", type=float, default=6e12,
+                    help="re-projection FLOPs of the host-core baseline's sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        if args.steps > 3:
+            args.steps = 3  # bounded: each step is seconds of host work
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
