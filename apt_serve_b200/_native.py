@@ -43,6 +43,8 @@ PROTOTYPES = {
     "aps_attention_workspace_bytes": (c_size_t, [c_int] * 5),
     "aps_paged_decode_attention": (c_int, [c_void_p] * 6 + [c_int] * 5 + [c_int64] * 3 +
                                    [c_float, c_void_p, c_size_t, c_int, c_void_p]),
+    "aps_paged_decode_attention_static": (c_int, [c_void_p] * 6 + [c_int] * 5 + [c_int64] * 3 +
+                                          [c_float, c_int, c_void_p]),
     "aps_hybrid_decode_attention": (c_int, [c_void_p] * 12 + [c_int] * 6 + [c_int64] * 6 +
                                     [c_float, c_void_p, c_size_t, c_int, c_void_p]),
     "aps_kv_reprojection": (c_int, [c_void_p] * 3 + [c_int64] + [c_void_p] * 4 + [c_int] * 3 +

@@ -384,3 +384,70 @@ extern "C" int aps_attention_status(const void* workspace, int* host_status, voi
   APS_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
   return APS_OK;
 }
+
+// ---- decode attention for callers that cannot allocate -----------------------------
+// The scratch of aps_paged_decode_attention_static lives in this module's image: a
+// fixed array in device memory that every GPU which loads the library holds until the
+// process exits.  Host code may not pass the array's name to a kernel (on the host it
+// is only a handle); the device address is looked up once per device with
+// cudaGetSymbolAddress, with that device current, and cached.
+namespace aps {
+namespace {
+
+constexpr size_t kStaticScratchBytes = size_t(32) << 20;  // 32 MiB
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+void* g_static_scratch_addr[64] = {nullptr};
+
+int static_scratch_address(void** out) {
+  int dev = 0;
+  APS_CUDA(cudaGetDevice(&dev));
+  APS_REQUIRE(dev >= 0 && dev < 64, APS_ERR_CUDA, "paged_decode_attention_static: device index %d out of range", dev);
+  if (g_static_scratch_addr[dev] == nullptr) {
+    void* p = nullptr;
+    APS_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+    APS_REQUIRE(p != nullptr && aligned_to(p, 256), APS_ERR_CUDA,
+                "paged_decode_attention_static: built-in scratch has no usable device address");
+    g_static_scratch_addr[dev] = p;
+  }
+  *out = g_static_scratch_addr[dev];
+  return APS_OK;
+}
+
+}  // namespace
+}  // namespace aps
+
+extern "C" int aps_paged_decode_attention_static(void* out, const void* query, const void* key_cache,
+                                                 const void* value_cache, const int32_t* block_tables,
+                                                 const int32_t* seq_lens, int batch,
+                                                 int max_blocks_per_seq, int num_heads, int head_size,
+                                                 int block_size, int64_t query_stride,
+                                                 int64_t out_stride, int64_t block_stride, float scale,
+                                                 int dtype, void* stream) {
+  APS_REQUIRE(batch >= 0 && max_blocks_per_seq > 0 && num_heads > 0 && head_size > 0 && block_size > 0,
+              APS_ERR_SHAPE, "paged_decode_attention_static: bad sizes");
+  const WorkspaceLayout w = workspace_layout(batch > 0 ? batch : 1, max_blocks_per_seq, block_size,
+                                             num_heads, head_size);
+  APS_REQUIRE(w.total <= kStaticScratchBytes, APS_ERR_WORKSPACE,
+              "paged_decode_attention_static: this batch needs %zu bytes of scratch but the built-in "
+              "scratch holds %zu (batch %d x %d blocks of %d tokens, %d heads x %d); use "
+              "aps_paged_decode_attention with a caller-provided workspace",
+              w.total, kStaticScratchBytes, batch, max_blocks_per_seq, block_size, num_heads, head_size);
+  AttnShape s{batch, max_blocks_per_seq, num_heads, head_size, block_size,
+              query_stride, out_stride, block_stride, scale, dtype};
+  // argument checks that do not touch the device come first; the scratch check inside
+  // check_attention_args is satisfied by construction
+  alignas(256) static unsigned char dummy_ws[256];
+  int st = check_attention_args("paged_decode_attention_static", out, query, key_cache, value_cache,
+                                block_tables, seq_lens, s, dummy_ws, w.total, true);
+  if (st != APS_OK || batch == 0) return st;
+  void* scratch = nullptr;
+  if ((st = static_scratch_address(&scratch)) != APS_OK) return st;
+  const WorkspacePtrs ws = workspace_ptrs(scratch, w);
+  cudaStream_t cs = (cudaStream_t)stream;
+  // plan_kernel rewrites every word of the scratch header (work counter, status word,
+  // list sizes) and every partial that the combine reads is rewritten by this call, so
+  // nothing left over from the previous call is ever read
+  if ((st = launch_plan(ws, seq_lens, nullptr, batch, max_blocks_per_seq, block_size, cs)) != APS_OK) return st;
+  if ((st = launch_kv_attention(ws, query, key_cache, value_cache, block_tables, seq_lens, s, cs)) != APS_OK) return st;
+  return launch_combine(ws, out, seq_lens, s, cs);
+}

@@ -160,6 +160,35 @@ int aps_paged_decode_attention(void* out, const void* query, const void* key_cac
                                void* stream);
 
 /*
+ * aps_paged_decode_attention for callers that cannot allocate device memory.
+ * This one has no counterpart in the reference.  Same arguments and result as
+ * aps_paged_decode_attention, minus the workspace: the scratch is a 32 MiB array
+ * built into the library's device image (each GPU that loads the library holds
+ * those 32 MiB until the process exits).  It serves hosts that bind this ABI
+ * without an allocator of their own -- a serving worker whose cache engine has
+ * already claimed all free HBM for K/V blocks, or a C / Go / Java host with no
+ * device-memory pool, for which a cudaMalloc per step would also stall the device.
+ *  - No cudaMalloc, cudaFree or allocating library call is made.
+ *  - A batch whose scratch need (aps_attention_workspace_bytes of its shape)
+ *    exceeds 32 MiB is rejected with APS_ERR_WORKSPACE; e.g. 64 requests x 2048
+ *    tokens at 40 heads x 128 need 21 MiB and fit, 256 such requests do not.
+ *  - The first call on each device looks up the array's device address
+ *    (cudaGetSymbolAddress, with that device current); make that first call
+ *    before any stream capture begins.
+ *  - All calls share the one array.  Everything a call reads from it is written
+ *    earlier in the same call (its first kernel resets the work counter, the list
+ *    sizes and the status word), so stale contents are harmless; but two calls
+ *    that overlap on the GPU (different streams, no ordering) race on it.
+ */
+int aps_paged_decode_attention_static(void* out, const void* query, const void* key_cache,
+                                      const void* value_cache, const int32_t* block_tables,
+                                      const int32_t* seq_lens, int batch,
+                                      int max_blocks_per_seq, int num_heads, int head_size,
+                                      int block_size, int64_t query_stride,
+                                      int64_t out_stride, int64_t block_stride, float scale,
+                                      int dtype, void* stream);
+
+/*
  * Hybrid decode attention: one call for the decode branch of
  * OPTAttention.forward with hidden-cached requests (opt.py:111-124: gather of
  * cached hidden rows, K/V re-projection lin.py:123-130) followed by the cache
