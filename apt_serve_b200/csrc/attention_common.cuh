@@ -23,6 +23,7 @@ enum PlanWord {
   kPlanKvCounter = 2,     // dynamic work counter of the K/V kernel
   kPlanHidCounter = 3,    // reserved
   kPlanStatus = 4,        // non-zero when a kernel gave up on a bounded wait
+  kPlanStatsWord = 16,    // 8 x 64-bit cycle counters of the re-projection kernel (debug aid)
   kPlanWords = 64
 };
 

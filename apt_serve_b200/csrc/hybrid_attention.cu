@@ -10,24 +10,33 @@
 // Here the hidden rows go HBM -> shared memory (TMA) -> tensor cores -> TMEM ->
 // registers -> softmax partial; K and V never exist in global memory.
 //
-// One work item = (M tile of 128 cached tokens of one hidden request, head h).
-// The CTA computes the 128 x 256 tile [K_h | V_h] = X_tile * [W_k,h ; W_v,h]^T
-// with fp32 accumulation in tensor memory:
+// One M tile = 128 cached tokens of one hidden request; for head h the tile's
+// 128 x 256 block [K_h | V_h] = X_tile * [W_k,h ; W_v,h]^T is accumulated in fp32 in
+// tensor memory.  Warp roles in every CTA:
 //   warp 0    TMA producer: per 64-element slab of the hidden dimension, one
 //             16-row box per cache block of the tile (hidden blocks are paged)
-//             and two 128-row boxes of W_k / W_v rows of head h, 128-byte swizzle,
-//             4-stage ring of 48 KB stages;
-//   warp 1    tcgen05.mma issuer (M=128, N=256, K=16 per instruction, 4 per
-//             slab), accumulators double-buffered in the 512 TMEM columns, so
-//             the main loop of item i+1 overlaps the epilogue of item i;
+//             plus the W rows of head h, 128-byte swizzle, multi-stage ring;
+//   warp 1    tcgen05.mma issuer (K = 16 per instruction, 4 per slab); the
+//             accumulator is double-buffered in the 512 TMEM columns, so the main
+//             loop of item i+1 overlaps the epilogue of item i;
 //   warps 2-5 epilogue: one thread per token row reads its K row from TMEM, adds
 //             b_k, dots with q (pre-scaled by scale*log2 e), block-wide max, then
 //             reads its V row, weighs it and column-sums over the 128 rows with a
 //             shuffle butterfly; the (max, sum, acc[128]) partial goes to scratch.
-// CTAs are persistent (one per SM) and walk the items in a rasterised order that
-// keeps 16 M tiles x ~9 heads in flight, so W_k|W_v slabs and hidden tiles are
-// shared through L2.  No cluster launch and no multicast: every CTA fetches its
-// own operands.
+//
+// Two variants of the main loop:
+//   single   one CTA per SM works alone: M128 N256 instructions, both W boxes
+//            loaded by the CTA, 4 stages of 48 KB.  Shared memory then carries
+//            96 B/clk of operand reads plus 96 B/clk of TMA writes.
+//   pair     two CTAs of a cluster (cta_group::2) work on two M tiles of the same
+//            head with one M256 N256 instruction stream issued by the even CTA:
+//            each CTA loads its own X tile and HALF of the W rows (even CTA: W_k,h,
+//            odd CTA: W_v,h), the tensor cores read both halves, 6 stages of 32 KB.
+//            Shared-memory traffic per SM drops to 64 + 64 B/clk.  Loads carry no
+//            multicast: each CTA fetches what it needs itself; the two CTAs
+//            only exchange mbarrier arrivals.
+// CTAs are persistent and walk the items in a rasterised order (a group of M tiles
+// x all heads) so that hidden tiles and W slabs are shared through L2.
 //
 // Every mbarrier wait is bounded by a clock budget; a wait that runs out records
 // a code in the plan's status word, tells the other warps through shared memory,
@@ -36,29 +45,39 @@
 #include "attention_common.cuh"
 
 #include <cuda.h>
+#include <stdlib.h>
+#include <string.h>
 #include <type_traits>
 
 namespace aps {
 namespace {
 
-constexpr int kBM = 128;          // token rows per tile
+constexpr int kBM = 128;          // token rows per tile (per CTA)
 constexpr int kBN = 256;          // K_h | V_h columns
 constexpr int kHeadDim = 128;
-constexpr int kBKBytes = 128;     // one swizzle row
-constexpr int kStages = 4;
+constexpr int kBKBytes = 128;     // one swizzle row = 64 two-byte elements
 constexpr int kABytes = kBM * kBKBytes;          // 16 KB
-constexpr int kBBytes = kBN * kBKBytes;          // 32 KB
-constexpr int kStageBytes = kABytes + kBBytes;   // 48 KB
 constexpr int kSubRows = 16;                     // rows per TMA box of the hidden cache
 constexpr int kSubBytes = kSubRows * kBKBytes;   // 2 KB
-constexpr int kThreads = 192;
-constexpr int kEpiThreads = 128;
-constexpr int kRasterTiles = 16;                 // M tiles per raster group
+constexpr int kSubsPerTile = kBM / kSubRows;     // 8
+constexpr int kThreads = 320;          // warps 0-1 TMA / MMA, 2-5 epilogue, 6-9 hidden-row loaders
+constexpr int kLoaderThreads = 128;
+constexpr int kMaxStages = 6;
 constexpr long long kWaitBudget = 4000000000LL;  // clock cycles (~2 s) before a wait gives up
 
+template <bool PAIR> struct Variant;
+template <> struct Variant<false> {
+  static constexpr int kStages = 4;
+  static constexpr int kBBytes = kBN * kBKBytes;       // 32 KB: W_k,h and W_v,h rows
+};
+template <> struct Variant<true> {
+  static constexpr int kStages = 6;
+  static constexpr int kBBytes = kBN / 2 * kBKBytes;   // 16 KB: this CTA's half of the W rows
+};
+
 struct SmemAux {
-  uint64_t full[kStages];
-  uint64_t empty[kStages];
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
   uint32_t tmem_base;
@@ -71,7 +90,11 @@ struct SmemAux {
   float red_acc[4][kHeadDim];
 };
 
-constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + (size_t)kStages * kStageBytes + sizeof(SmemAux);
+template <bool PAIR>
+constexpr size_t smem_bytes() {
+  return 1024 /*alignment slack*/ +
+         (size_t)Variant<PAIR>::kStages * (kABytes + Variant<PAIR>::kBBytes) + sizeof(SmemAux);
+}
 
 // ---- PTX wrappers --------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -85,6 +108,10 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 }
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Arrive on a barrier given by its shared::cluster address (own CTA or the peer).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
@@ -113,6 +140,20 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
   return true;
 }
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of `addr` (a shared::cta address of this CTA) in CTA `rank`.
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar,
                                             int x, int y) {
   asm volatile(
@@ -120,10 +161,23 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
 }
+// Load into this CTA's shared memory, completion bytes counted on a barrier that
+// may live in the peer CTA of the pair (given as a shared::cluster address).
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map,
+                                                 uint32_t bar_cluster_addr, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Pair variant: the barrier is named by a shared::cluster address (own CTA or peer).
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
 __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                            uint32_t idesc, uint32_t accumulate) {
@@ -131,6 +185,14 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uin
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
@@ -168,9 +230,9 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
 }
 
 // kind::f16 instruction descriptor: fp32 accumulate, A/B format fmt (0 = f16,
-// 1 = bf16), both K-major, N = 256, M = 128.
-__host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt) {
-  return (1u << 4) | (fmt << 7) | (fmt << 10) | ((kBN >> 3) << 17) | ((kBM >> 4) << 24);
+// 1 = bf16), both K-major, N = 256, M = m (128 for one CTA, 256 for a pair).
+__host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt, uint32_t m) {
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | ((kBN >> 3) << 17) | ((m >> 4) << 24);
 }
 
 // ---- work items -----------------------------------------------------------------
@@ -201,19 +263,77 @@ struct HiddenParams {
   const void* b_v;
   int heads;
   int k_slabs;                // ceil(hidden_size / 64)
+  int raster_units;           // units per group of the work order (see item_of)
+  int raster_heads;           // heads per group of the work order
+  int dense_a;                // X rows of a tile are contiguous: map_x has a 128-row box
+  int a_mode;                 // 0: hidden rows by TMA boxes, 1: by the loader warps (cp.async)
+  int b_skip;                 // timing experiment only: do not load W (results are garbage)
+  int debug;                  // timing experiments only: bit 0 skip epilogue math, bit 1 producer ignores empty
+  int hidden_mult64;          // hidden size is a multiple of 64 elements
+  const void* x_base;         // first row of the hidden cache / X matrix (a_mode 1)
+  int64_t x_row_bytes;        // its row stride in bytes
+  int64_t x_rows;             // number of addressable rows (rows past it read as zeros)
+  unsigned long long* stats;  // optional cycle counters (nullptr = off): see aps_hybrid_decode_attention
   int* status;
 };
 
-struct Item { int tile, head; };
+struct Item { int unit, head; };   // unit = M tile (single) or tile pair (pair variant)
 
-__device__ __forceinline__ Item item_of(int i, int n_tiles, int heads) {
-  const int per_group = kRasterTiles * heads;
-  const int g = i / per_group, within = i - g * per_group;
-  const int gm = min(kRasterTiles, n_tiles - g * kRasterTiles);
+// Work order.  Heads are taken in groups of `rh`; inside a head group the units (M tiles
+// or tile pairs) are taken in groups of `ru`; inside such a block the order is head-major.
+// While a head group is being worked on its W rows (rh x 2 x 128 x E elements) stay hot in
+// L2 across all unit groups, and the hidden rows of a unit group are fetched from HBM once
+// per head group and reused from L2 by the group's other heads.
+__device__ __forceinline__ Item item_of(int i, int n_units, int heads, int ru, int rh) {
+  const int per_hg = n_units * rh;
+  const int hg = i / per_hg;
+  const int rem = i - hg * per_hg;
+  const int hsz = min(rh, heads - hg * rh);
+  const int per_block = ru * hsz;
+  const int ug = rem / per_block;
+  const int within = rem - ug * per_block;
+  const int gm = min(ru, n_units - ug * ru);
+  const int hl = within / gm;
   Item it;
-  it.head = within / gm;
-  it.tile = g * kRasterTiles + within - it.head * gm;
+  it.head = hg * rh + hl;
+  it.unit = ug * ru + within - hl * gm;
   return it;
+}
+
+// Valid rows of M tile `tile` (0 when the tile does not exist).
+template <int MODE>
+__device__ __forceinline__ int tile_valid_rows(const HiddenParams& p, int tile, int n_tiles) {
+  if (tile >= n_tiles) return 0;
+  if (MODE == kModeAttend) {
+    const int2 rc = p.hid_tiles[tile];
+    const int seq = min(p.seq_lens[rc.x], p.max_blocks_per_seq * p.block_size);
+    return min(kBM, seq - rc.y * kBM);
+  }
+  return (int)min((int64_t)kBM, p.n_rows - (int64_t)tile * kBM);
+}
+
+// First hidden-cache row of each 16-row sub-block of a tile.
+template <int MODE>
+__device__ __forceinline__ void tile_sub_rows(const HiddenParams& p, int tile, int n_sub, int* sub_row) {
+  if (MODE == kModeAttend) {
+    const int2 rc = p.hid_tiles[tile < 0 ? 0 : tile];
+    const int32_t* bt = p.block_tables + (int64_t)rc.x * p.max_blocks_per_seq;
+    const int tok0 = rc.y * kBM;
+#pragma unroll
+    for (int j = 0; j < kSubsPerTile; ++j) {
+      const int tok = tok0 + j * kSubRows;
+      sub_row[j] = j < n_sub ? bt[tok / p.block_size] * p.block_size + tok % p.block_size : 0;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < kSubsPerTile; ++j) {
+      if (j < n_sub)
+        sub_row[j] = p.block_ids ? p.block_ids[tile * kSubsPerTile + j] * kSubRows
+                                 : tile * kBM + j * kSubRows;
+      else
+        sub_row[j] = 0;
+    }
+  }
 }
 
 // Butterfly column sum: on return v[0] of lane L holds the sum over the warp's
@@ -232,81 +352,228 @@ __device__ __forceinline__ void warp_column_sum(float* v, int lane) {
   }
 }
 
+// ---- epilogue (the 128 threads of warps 2..5) --------------------------------------
+// Before the accumulator is ready: stage q (attend mode) and the biases of head `head`.
 template <typename T, int MODE>
+__device__ __forceinline__ void epilogue_stage_inputs(SmemAux* aux, const HiddenParams& p, int tile,
+                                                      bool tile_ok, int head, int et) {
+  const int hcol = head * kHeadDim;
+  const T* bk = static_cast<const T*>(p.b_k);
+  const T* bv = static_cast<const T*>(p.b_v);
+  if (MODE == kModeAttend) {
+    float qv = 0.f;
+    if (tile_ok) {
+      const int req = p.hid_tiles[tile].x;
+      const T* q = static_cast<const T*>(p.query) + req * p.query_stride + hcol;
+      qv = Elem<T>::to_float(q[et]) * p.scale_log2;
+    }
+    aux->q[et] = qv;
+  }
+  aux->bk[et] = bk ? Elem<T>::to_float(bk[hcol + et]) : 0.f;
+  aux->bv[et] = bv ? Elem<T>::to_float(bv[hcol + et]) : 0.f;
+  epi_barrier();
+}
+
+// After the accumulator is ready.  `release()` is called once, when this thread's
+// last TMEM read has completed.
+template <typename T, int MODE, typename Release>
+__device__ __forceinline__ void epilogue_compute(SmemAux* aux, const HiddenParams& p, uint32_t t_row,
+                                                 int tile, bool tile_ok, int head, int quarter,
+                                                 int lane, int et, Release release) {
+  const int row = quarter * 32 + lane;
+  const int hcol = head * kHeadDim;
+  uint32_t r[32];
+
+  if (MODE == kModeStore) {
+    const int64_t out_row = (int64_t)tile * kBM + row;
+    const bool valid = tile_ok && out_row < p.n_rows;
+    T* dst_k = static_cast<T*>(p.kv_out) + out_row * p.kv_stride + hcol;
+    T* dst_v = dst_k + (int64_t)p.heads * kHeadDim;
+#pragma unroll 1
+    for (int c = 0; c < 8; ++c) {
+      tmem_ld32(t_row + c * 32, r);
+      tmem_ld_wait();
+      const float* bias = c < 4 ? aux->bk : aux->bv;
+      T* dst = (c < 4 ? dst_k : dst_v) + (c & 3) * 32;
+      if (valid) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          T tmp[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e)
+            tmp[e] = Elem<T>::from_float(__uint_as_float(r[j + e]) + bias[(c & 3) * 32 + j + e]);
+          *reinterpret_cast<uint4*>(dst + j) = *reinterpret_cast<const uint4*>(tmp);
+        }
+      }
+    }
+    release();
+    epi_barrier();  // the bias buffers are rewritten by the next item
+    return;
+  }
+
+  int req = 0, chunk = 0;
+  bool valid = false;
+  if (tile_ok) {
+    const int2 rc = p.hid_tiles[tile];
+    req = rc.x; chunk = rc.y;
+    const int seq = min(p.seq_lens[req], p.max_blocks_per_seq * p.block_size);
+    valid = chunk * kBM + row < seq;
+  }
+  // ---- scores: s = q . (K_row + b_k), already in the log2 domain ----
+  float s = 0.f;
+#pragma unroll 1
+  for (int c = 0; c < 4; ++c) {
+    tmem_ld32(t_row + c * 32, r);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      s = fmaf(aux->q[c * 32 + j], __uint_as_float(r[j]) + aux->bk[c * 32 + j], s);
+  }
+  s = valid ? s : -INFINITY;
+  float wm = s;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, o));
+  if (lane == 0) aux->red_max[quarter] = wm;
+  epi_barrier();
+  const float mx = fmaxf(fmaxf(aux->red_max[0], aux->red_max[1]), fmaxf(aux->red_max[2], aux->red_max[3]));
+  const float pr = valid ? exp2f(s - mx) : 0.f;
+  float ws = pr;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ws += __shfl_xor_sync(0xffffffffu, ws, o);
+  if (lane == 0) aux->red_sum[quarter] = ws;
+
+  // ---- weighted V rows, column sums over the warp's 32 rows ----
+#pragma unroll 1
+  for (int c = 0; c < 4; ++c) {
+    tmem_ld32(t_row + kHeadDim + c * 32, r);
+    tmem_ld_wait();
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      v[j] = valid ? pr * (__uint_as_float(r[j]) + aux->bv[c * 32 + j]) : 0.f;
+    warp_column_sum(v, lane);
+    aux->red_acc[quarter][c * 32 + lane] = v[0];
+  }
+  release();
+  epi_barrier();
+  if (tile_ok) {
+    const float a = aux->red_acc[0][et] + aux->red_acc[1][et] + aux->red_acc[2][et] + aux->red_acc[3][et];
+    const int64_t slot = (int64_t)(p.part_offset[req] + chunk) * p.heads + head;
+    p.part_acc[slot * kHeadDim + et] = a;
+    if (et == 0) {
+      const float l = aux->red_sum[0] + aux->red_sum[1] + aux->red_sum[2] + aux->red_sum[3];
+      *reinterpret_cast<float2*>(p.part_ml + slot * 2) = make_float2(mx, l);
+    }
+  }
+}
+
+// ---- the kernel ---------------------------------------------------------------------
+template <typename T, int MODE, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_wk,
                    const __grid_constant__ CUtensorMap map_wv, const HiddenParams p) {
+  using V = Variant<PAIR>;
+  constexpr int kStages = V::kStages;
+  constexpr int kStageBytes = kABytes + V::kBBytes;
+
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   SmemAux* aux = reinterpret_cast<SmemAux*>(smem + (size_t)kStages * kStageBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* abort_flag = &aux->abort_flag;
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;   // position in the CTA pair
+  const bool leader = rank == 0;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) { mbar_init(&aux->full[s], 1); mbar_init(&aux->empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&aux->acc_full[b], 1); mbar_init(&aux->acc_empty[b], 4); }
+    // full[s]: one arrival from the TMA producer (with the byte count of its boxes), plus one
+    // per loader thread when the hidden rows are brought in by the loader warps
+    const uint32_t full_count = 1u + ((!PAIR && p.a_mode >= 1) ? (uint32_t)kLoaderThreads : 0u);
+    for (int s = 0; s < kStages; ++s) { mbar_init(&aux->full[s], full_count); mbar_init(&aux->empty[s], 1); }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&aux->acc_full[b], 1);
+      mbar_init(&aux->acc_empty[b], PAIR ? 8 : 4);   // one arrival per epilogue warp (of both CTAs)
+    }
     aux->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(&aux->tmem_base)) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (PAIR) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(&aux->tmem_base)) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(&aux->tmem_base)) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();   // the peer's barriers are initialised before anyone signals them
   tc_fence_after();
   const uint32_t tmem_base = aux->tmem_base;
 
   const int n_tiles = MODE == kModeAttend ? p.plan[kPlanNumHidTiles] : p.n_store_tiles;
-  const int n_items = n_tiles * p.heads;
+  const int n_units = PAIR ? (n_tiles + 1) / 2 : n_tiles;
+  const int n_items = n_units * p.heads;
+  const int first = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int stride = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
   if (warp == 0) {
     // ===================== TMA producer =====================
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (int i = blockIdx.x; i < n_items && ok; i += gridDim.x) {
-        const Item it = item_of(i, n_tiles, p.heads);
-        int n_sub;
-        int sub_row[kBM / kSubRows];
-        if (MODE == kModeAttend) {
-          const int2 rc = p.hid_tiles[it.tile];
-          const int seq = min(p.seq_lens[rc.x], p.max_blocks_per_seq * p.block_size);
-          const int tok0 = rc.y * kBM;
-          const int valid = min(kBM, seq - tok0);
-          n_sub = (valid + kSubRows - 1) / kSubRows;
-          const int32_t* bt = p.block_tables + (int64_t)rc.x * p.max_blocks_per_seq;
-#pragma unroll
-          for (int j = 0; j < kBM / kSubRows; ++j) {
-            const int tok = tok0 + j * kSubRows;
-            sub_row[j] = j < n_sub ? bt[tok / p.block_size] * p.block_size + tok % p.block_size : 0;
-          }
-        } else {
-          const int64_t row0 = (int64_t)it.tile * kBM;
-          const int valid = (int)min((int64_t)kBM, p.n_rows - row0);
-          n_sub = (valid + kSubRows - 1) / kSubRows;
-#pragma unroll
-          for (int j = 0; j < kBM / kSubRows; ++j) {
-            if (j < n_sub)
-              sub_row[j] = p.block_ids ? p.block_ids[it.tile * (kBM / kSubRows) + j] * kSubRows
-                                       : (int)(row0 + j * kSubRows);
-            else
-              sub_row[j] = 0;
-          }
+      const bool loaders = !PAIR && p.a_mode >= 1;   // hidden rows come from the loader warps
+      long long w_empty = 0;
+      for (int i = first; i < n_items && ok; i += stride) {
+        const Item it = item_of(i, n_units, p.heads, p.raster_units, p.raster_heads);
+        const int tile = PAIR ? it.unit * 2 + (int)rank : it.unit;
+        const int n_sub = (loaders || p.a_mode == 3) ? 0 : (tile_valid_rows<MODE>(p, tile, n_tiles) + kSubRows - 1) / kSubRows;
+        int sub_row[kSubsPerTile];
+        tile_sub_rows<MODE>(p, n_sub > 0 ? tile : 0, n_sub, sub_row);
+        // a dense X tile is one 128-row box (rows past the end are zero-filled and still
+        // counted); a paged tile is one 16-row box per cache block in use
+        const bool dense = p.dense_a != 0;
+        uint32_t tx_bytes = (uint32_t)((dense ? (n_sub > 0 ? kABytes : 0) : n_sub * kSubBytes) + V::kBBytes);
+        if (PAIR && leader) {
+          const int peer_sub = p.a_mode == 3 ? 0 : (tile_valid_rows<MODE>(p, tile + 1, n_tiles) + kSubRows - 1) / kSubRows;
+          tx_bytes += (uint32_t)((dense ? (peer_sub > 0 ? kABytes : 0) : peer_sub * kSubBytes) + V::kBBytes);
+          if (p.b_skip) tx_bytes -= 2 * V::kBBytes;
         }
-        const uint32_t tx_bytes = (uint32_t)(n_sub * kSubBytes + kBBytes);
         for (int ks = 0; ks < p.k_slabs; ++ks) {
-          if (!mbar_wait(&aux->empty[stage], phase ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
+          const long long t0 = p.stats ? clock64() : 0;
+          if (!(p.debug & 2) && !mbar_wait(&aux->empty[stage], phase ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
+          if (p.stats) w_empty += clock64() - t0;
           uint8_t* a_dst = smem + (size_t)stage * kStageBytes;
           uint8_t* b_dst = a_dst + kABytes;
-          mbar_expect_tx(&aux->full[stage], tx_bytes);
           const int x = ks * (kBKBytes / (int)sizeof(T));
+          if (PAIR) {
+            // bytes of both CTAs are counted on the even CTA's barrier
+            if (leader) mbar_expect_tx(&aux->full[stage], tx_bytes);
+            const uint32_t bar = mapa_u32(smem_u32(&aux->full[stage]), 0);
+            if (dense) {
+              if (n_sub > 0) tma_load_2d_pair(a_dst, &map_x, bar, x, tile * kBM);
+            } else {
 #pragma unroll
-          for (int j = 0; j < kBM / kSubRows; ++j)
-            if (j < n_sub) tma_load_2d(a_dst + j * kSubBytes, &map_x, &aux->full[stage], x, sub_row[j]);
-          tma_load_2d(b_dst, &map_wk, &aux->full[stage], x, it.head * kHeadDim);
-          tma_load_2d(b_dst + kBBytes / 2, &map_wv, &aux->full[stage], x, it.head * kHeadDim);
+              for (int j = 0; j < kSubsPerTile; ++j)
+                if (j < n_sub) tma_load_2d_pair(a_dst + j * kSubBytes, &map_x, bar, x, sub_row[j]);
+            }
+            if (!p.b_skip) tma_load_2d_pair(b_dst, leader ? &map_wk : &map_wv, bar, x, it.head * kHeadDim);
+          } else {
+            if (p.b_skip) { mbar_expect_tx(&aux->full[stage], tx_bytes - V::kBBytes); }
+            else mbar_expect_tx(&aux->full[stage], tx_bytes);
+            if (dense) {
+              if (n_sub > 0) tma_load_2d(a_dst, &map_x, &aux->full[stage], x, tile * kBM);
+            } else {
+#pragma unroll
+              for (int j = 0; j < kSubsPerTile; ++j)
+                if (j < n_sub) tma_load_2d(a_dst + j * kSubBytes, &map_x, &aux->full[stage], x, sub_row[j]);
+            }
+            if (!p.b_skip) {
+              tma_load_2d(b_dst, &map_wk, &aux->full[stage], x, it.head * kHeadDim);
+              tma_load_2d(b_dst + V::kBBytes / 2, &map_wv, &aux->full[stage], x, it.head * kHeadDim);
+            }
+          }
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }
@@ -316,155 +583,170 @@ hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         const long long t0 = clock64();
         while (clock64() - t0 < 2000000LL) { }
       }
+      if (p.stats) atomicAdd(p.stats + 3, (unsigned long long)w_empty);
     }
     __syncwarp();
   } else if (warp == 1) {
-    // ===================== MMA issuer =====================
-    if (lane == 0) {
-      const uint32_t idesc = instr_desc(sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1u : 0u);
+    // ===================== MMA issuer (the even CTA of a pair issues for both) =====================
+    if (lane == 0 && leader) {
+      const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+      const uint32_t idesc = instr_desc(fmt, PAIR ? 256u : 128u);
       uint32_t stage = 0, phase = 0, n_local = 0;
       bool ok = true;
-      for (int i = blockIdx.x; i < n_items && ok; i += gridDim.x, ++n_local) {
+      const bool st = p.stats != nullptr;
+      long long t_begin = st ? clock64() : 0, w_full = 0, w_acc = 0, w_first = 0;
+      for (int i = first; i < n_items && ok; i += stride, ++n_local) {
         const uint32_t buf = n_local & 1u, use = n_local >> 1;
+        long long t0 = st ? clock64() : 0;
         if (!mbar_wait(&aux->acc_empty[buf], (use & 1u) ^ 1u, abort_flag, p.status, 2)) { ok = false; break; }
+        if (st) w_acc += clock64() - t0;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * kBN;
         for (int ks = 0; ks < p.k_slabs; ++ks) {
-          if (!mbar_wait(&aux->full[stage], phase, abort_flag, p.status, 3)) { ok = false; break; }
+          t0 = st ? clock64() : 0;
+          if (!(p.debug & 4) && !mbar_wait(&aux->full[stage], phase, abort_flag, p.status, 3)) { ok = false; break; }
+          if (st) { const long long dt = clock64() - t0; w_full += dt; if (ks == 0) w_first += dt; }
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(smem + (size_t)stage * kStageBytes);
+          const uint32_t a_addr = smem_u32(smem + (size_t)((p.debug & 8) ? 0 : stage) * kStageBytes);
           const uint64_t a_desc = smem_desc_sw128(a_addr);
           const uint64_t b_desc = smem_desc_sw128(a_addr + kABytes);
 #pragma unroll
-          for (int k = 0; k < kBKBytes / 32; ++k)
-            tc_mma_f16(d_tmem, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc,
-                       (ks | k) != 0 ? 1u : 0u);
-          tc_commit(&aux->empty[stage]);
+          for (int k = 0; k < kBKBytes / 32; ++k) {
+            if (PAIR)
+              tc_mma_f16_pair(d_tmem, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc,
+                              (ks | k) != 0 ? 1u : 0u);
+            else
+              tc_mma_f16(d_tmem, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc,
+                         (ks | k) != 0 ? 1u : 0u);
+          }
+          if (PAIR) {
+            // release the stage in both CTAs
+            const uint32_t e = smem_u32(&aux->empty[stage]);
+            tc_commit_pair(mapa_u32(e, 0));
+            tc_commit_pair(mapa_u32(e, 1));
+          } else {
+            tc_commit(&aux->empty[stage]);
+          }
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
-        if (ok) tc_commit(&aux->acc_full[buf]);
+        if (ok) {
+          if (PAIR) {
+            const uint32_t f = smem_u32(&aux->acc_full[buf]);
+            tc_commit_pair(mapa_u32(f, 0));
+            tc_commit_pair(mapa_u32(f, 1));
+          } else {
+            tc_commit(&aux->acc_full[buf]);
+          }
+        }
+      }
+      if (st) {
+        atomicAdd(p.stats + 0, (unsigned long long)(clock64() - t_begin));
+        atomicAdd(p.stats + 1, (unsigned long long)w_full);
+        atomicAdd(p.stats + 2, (unsigned long long)w_acc);
+        atomicAdd(p.stats + 6, (unsigned long long)n_local);
+        atomicAdd(p.stats + 7, (unsigned long long)w_first);
       }
     }
     __syncwarp();
+  } else if (warp >= 6) {
+    // ===================== hidden-row loaders (warps 6..9) =====================
+    // A TMA box costs the copy engine a fixed ~25 ns whatever its size, and a paged tile
+    // needs eight 16-row boxes per slab, which alone holds the main loop near 60 % of its
+    // dense rate.  So the paged hidden rows are brought in with plain 16-byte asynchronous
+    // copies instead: thread t copies 16-byte column chunk (t % 8) of row (t / 8) of every
+    // cache block of the tile into the 128-byte-swizzled stage (chunk index XOR row % 8),
+    // and the stage's barrier counts one arrival per thread, delivered by the copy unit when
+    // that thread's copies have landed.  The W boxes stay on TMA.
+    if (!PAIR && p.a_mode >= 1) {
+      const int t = (int)threadIdx.x - (kThreads - kLoaderThreads);
+      const int r16 = t >> 3, col = t & 7;
+      const uint32_t swz = (uint32_t)(r16 * kBKBytes + ((col ^ (r16 & 7)) << 4));
+      const char* xb = static_cast<const char*>(p.x_base);
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int i = first; i < n_items && ok; i += stride) {
+        const Item it = item_of(i, n_units, p.heads, p.raster_units, p.raster_heads);
+        const int tile = it.unit;
+        const int n_sub = (tile_valid_rows<MODE>(p, tile, n_tiles) + kSubRows - 1) / kSubRows;
+        int sub_row[kSubsPerTile];
+        tile_sub_rows<MODE>(p, n_sub > 0 ? tile : 0, n_sub, sub_row);
+        const char* src[kSubsPerTile];
+        uint32_t in_range = 0;   // bit c: the row of sub-block c exists (else zero-fill)
+#pragma unroll
+        for (int c = 0; c < kSubsPerTile; ++c) {
+          const int64_t row = (int64_t)sub_row[c] + r16;
+          const bool okr = row < p.x_rows;
+          in_range |= (okr ? 1u : 0u) << c;
+          src[c] = xb + (okr ? row : 0) * p.x_row_bytes + col * 16;
+        }
+        for (int ks = 0; ks < p.k_slabs; ++ks) {
+          {
+            const bool got = lane != 0 || mbar_wait(&aux->empty[stage], phase ^ 1, abort_flag, p.status, 5);
+            ok = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0;   // lane 0 polls for the warp
+            if (!ok) break;
+          }
+          const uint32_t dst = smem_u32(smem + (size_t)stage * kStageBytes) + swz;
+#pragma unroll
+          for (int c = 0; c < kSubsPerTile; ++c)
+            if (c < n_sub && p.a_mode == 1)
+              asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + c * kSubBytes),
+                           "l"(src[c] + (int64_t)ks * kBKBytes), "r"(((in_range >> c) & 1u) * 16u) : "memory");
+          // arrives on the stage's barrier when this thread's copies above have landed
+          asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&aux->full[stage])) : "memory");
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+      // the copies issued last must land before the CTA's shared memory is released
+      asm volatile("cp.async.wait_all;" ::: "memory");
+    }
   } else {
     // ===================== epilogue (warps 2..5) =====================
     const int quarter = warp & 3;               // TMEM lanes this warp may read
-    const int row = quarter * 32 + lane;        // token row inside the tile
-    const int et = threadIdx.x - 64;            // 0..127 (column owner in the final step)
-    const T* bk = static_cast<const T*>(p.b_k);
-    const T* bv = static_cast<const T*>(p.b_v);
+    const int et = threadIdx.x - 64;            // 0..127
     uint32_t n_local = 0;
     bool ok = true;
-    for (int i = blockIdx.x; i < n_items && ok; i += gridDim.x, ++n_local) {
-      const Item it = item_of(i, n_tiles, p.heads);
+    for (int i = first; i < n_items && ok; i += stride, ++n_local) {
+      const Item it = item_of(i, n_units, p.heads, p.raster_units, p.raster_heads);
+      const int tile = PAIR ? it.unit * 2 + (int)rank : it.unit;
+      const bool tile_ok = tile < n_tiles;
       const uint32_t buf = n_local & 1u, use = n_local >> 1;
-      const int hcol = it.head * kHeadDim;
-      bool valid;
-      int req = 0, chunk = 0;
-      int64_t out_row = 0;
-      if (MODE == kModeAttend) {
-        const int2 rc = p.hid_tiles[it.tile];
-        req = rc.x; chunk = rc.y;
-        const int seq = min(p.seq_lens[req], p.max_blocks_per_seq * p.block_size);
-        valid = chunk * kBM + row < seq;
-        const T* q = static_cast<const T*>(p.query) + req * p.query_stride + hcol;
-        aux->q[et] = Elem<T>::to_float(q[et]) * p.scale_log2;
-      } else {
-        out_row = (int64_t)it.tile * kBM + row;
-        valid = out_row < p.n_rows;
-      }
-      aux->bk[et] = bk ? Elem<T>::to_float(bk[hcol + et]) : 0.f;
-      aux->bv[et] = bv ? Elem<T>::to_float(bv[hcol + et]) : 0.f;
-      epi_barrier();
-
-      if (!epi_all(mbar_wait(&aux->acc_full[buf], use & 1u, abort_flag, p.status, 4))) { ok = false; break; }
+      epilogue_stage_inputs<T, MODE>(aux, p, tile, tile_ok, it.head, et);
+      const long long t0 = (p.stats && et == 0) ? clock64() : 0;
+      // one lane per warp polls the barrier; the other 124 threads wait in the hardware
+      // barrier of epi_all (polling by every thread floods the SM's mbarrier unit and slows
+      // the producer / MMA handshake down)
+      const bool got = lane != 0 || mbar_wait(&aux->acc_full[buf], use & 1u, abort_flag, p.status, 4);
+      if (!epi_all(got)) { ok = false; break; }
+      const long long t1 = (p.stats && et == 0) ? clock64() : 0;
       tc_fence_after();
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * kBN;
-      uint32_t r[32];
-
-      if (MODE == kModeStore) {
-        T* dst_k = static_cast<T*>(p.kv_out) + out_row * p.kv_stride + hcol;
-        T* dst_v = dst_k + (int64_t)p.heads * kHeadDim;
-#pragma unroll 1
-        for (int c = 0; c < 8; ++c) {
-          tmem_ld32(t_row + c * 32, r);
-          tmem_ld_wait();
-          const float* bias = c < 4 ? aux->bk : aux->bv;
-          T* dst = (c < 4 ? dst_k : dst_v) + (c & 3) * 32;
-          if (valid) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              T tmp[8];
-#pragma unroll
-              for (int e = 0; e < 8; ++e)
-                tmp[e] = Elem<T>::from_float(__uint_as_float(r[j + e]) + bias[(c & 3) * 32 + j + e]);
-              *reinterpret_cast<uint4*>(dst + j) = *reinterpret_cast<const uint4*>(tmp);
-            }
-          }
-        }
+      uint64_t* acc_empty = &aux->acc_empty[buf];
+      auto release = [&]() {
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&aux->acc_empty[buf]);
-        epi_barrier();  // bias buffers are rewritten by the next item
-        continue;
-      }
-
-      // ---- scores: s = q . (K_row + b_k), already in the log2 domain ----
-      float s = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        tmem_ld32(t_row + c * 32, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-          s = fmaf(aux->q[c * 32 + j], __uint_as_float(r[j]) + aux->bk[c * 32 + j], s);
-      }
-      s = valid ? s : -INFINITY;
-      float wm = s;
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, o));
-      if (lane == 0) aux->red_max[quarter] = wm;
-      epi_barrier();
-      const float mx = fmaxf(fmaxf(aux->red_max[0], aux->red_max[1]), fmaxf(aux->red_max[2], aux->red_max[3]));
-      const float pr = valid ? exp2f(s - mx) : 0.f;
-      float ws = pr;
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) ws += __shfl_xor_sync(0xffffffffu, ws, o);
-      if (lane == 0) aux->red_sum[quarter] = ws;
-
-      // ---- weighted V rows, column sums over the warp's 32 rows ----
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        tmem_ld32(t_row + kHeadDim + c * 32, r);
-        tmem_ld_wait();
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-          v[j] = valid ? pr * (__uint_as_float(r[j]) + aux->bv[c * 32 + j]) : 0.f;
-        warp_column_sum(v, lane);
-        aux->red_acc[quarter][c * 32 + lane] = v[0];
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&aux->acc_empty[buf]);
-      epi_barrier();
-      {
-        const float a = aux->red_acc[0][et] + aux->red_acc[1][et] + aux->red_acc[2][et] + aux->red_acc[3][et];
-        const int64_t slot = (int64_t)(p.part_offset[req] + chunk) * p.heads + it.head;
-        p.part_acc[slot * kHeadDim + et] = a;
-        if (et == 0) {
-          const float l = aux->red_sum[0] + aux->red_sum[1] + aux->red_sum[2] + aux->red_sum[3];
-          *reinterpret_cast<float2*>(p.part_ml + slot * 2) = make_float2(mx, l);
+        if (lane == 0) {
+          if (PAIR) mbar_arrive_cluster(mapa_u32(smem_u32(acc_empty), 0));
+          else mbar_arrive(acc_empty);
         }
+      };
+      if (p.debug & 1) { release(); epi_barrier(); }
+      else epilogue_compute<T, MODE>(aux, p, t_row, tile, tile_ok, it.head, quarter, lane, et, release);
+      if (p.stats && et == 0) {
+        atomicAdd(p.stats + 4, (unsigned long long)(t1 - t0));
+        atomicAdd(p.stats + 5, (unsigned long long)(clock64() - t1));
       }
     }
   }
 
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();   // nobody leaves while the peer may still read its memory or signal it
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+    if (PAIR)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
   }
 }
 
@@ -503,22 +785,84 @@ int make_map(CUtensorMap* map, const void* base, int dtype, uint64_t cols, uint6
   return APS_OK;
 }
 
-template <typename T, int MODE>
-int launch_hidden(const CUtensorMap& mx, const CUtensorMap& mk, const CUtensorMap& mv,
-                  const HiddenParams& p, cudaStream_t stream) {
-  static bool configured[64] = {false};
+// Which main-loop variant to run: APS_HIDDEN_VARIANT=single|pair overrides the default.
+bool use_pair_variant() {
+  const char* v = getenv("APS_HIDDEN_VARIANT");
+  if (v != nullptr && strcmp(v, "single") == 0) return false;
+  if (v != nullptr && strcmp(v, "pair") == 0) return true;
+  return true;
+}
+
+template <typename T, int MODE, bool PAIR>
+int launch_hidden_variant(const CUtensorMap& mx, const CUtensorMap& mk, const CUtensorMap& mv,
+                          const HiddenParams& p, cudaStream_t stream) {
+  static int grid_for_device[64] = {0};
   int dev = 0;
   APS_CUDA(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !configured[dev]) {
-    APS_CUDA(cudaFuncSetAttribute(hidden_path_kernel<T, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  (int)kSmemBytes));
-    configured[dev] = true;
+  APS_REQUIRE(dev >= 0 && dev < 64, APS_ERR_CUDA, "device index %d out of range", dev);
+  auto kernel = hidden_path_kernel<T, MODE, PAIR>;
+  constexpr size_t smem = smem_bytes<PAIR>();
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (PAIR) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
   }
+  if (grid_for_device[dev] == 0) {
+    APS_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    int grid = sm_count();
+    if (PAIR) {
+      // one CTA per SM, in pairs: as many pairs as the device can keep resident at once
+      cfg.gridDim = dim3((unsigned)(grid & ~1));
+      int clusters = 0;
+      APS_CUDA(cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg));
+      APS_REQUIRE(clusters > 0, APS_ERR_CUDA, "no CTA pair of the re-projection kernel fits on this device");
+      grid = 2 * (clusters < grid / 2 ? clusters : grid / 2);
+    }
+    grid_for_device[dev] = grid;
+  }
+  cfg.gridDim = dim3((unsigned)grid_for_device[dev]);
   {
     ScopedProfile prof(1, stream);
-    hidden_path_kernel<T, MODE><<<sm_count(), kThreads, kSmemBytes, stream>>>(mx, mk, mv, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, mx, mk, mv, p);
+    if (e != cudaSuccess)
+      return fail(APS_ERR_CUDA, "launch of hidden_path_kernel failed: %s", cudaGetErrorString(e));
   }
   return launch_status("hidden_path_kernel");
+}
+
+// Work-order group sizes: APS_RASTER="units,heads" overrides the default.
+void raster_sizes(int* units, int* heads) {
+  *units = 16; *heads = 8;
+  const char* v = getenv("APS_RASTER");
+  if (v != nullptr) {
+    int a = 0, b = 0;
+    if (sscanf(v, "%d,%d", &a, &b) == 2 && a > 0 && b > 0) { *units = a; *heads = b; }
+  }
+}
+
+template <typename T, int MODE>
+int launch_hidden(const CUtensorMap& mx, const CUtensorMap& mk, const CUtensorMap& mv,
+                  HiddenParams p, cudaStream_t stream) {
+  raster_sizes(&p.raster_units, &p.raster_heads);
+  if (p.raster_heads > p.heads) p.raster_heads = p.heads;
+  // hidden rows come in as TMA boxes; APS_A_MODE=loaders (single-CTA variant only) brings
+  // paged rows in with the loader warps instead, which needs a hidden size that is a whole
+  // number of 64-element slabs (TMA zero-fills a ragged tail, plain copies cannot)
+  const char* am = getenv("APS_A_MODE");
+  const bool want_loaders = am != nullptr && strcmp(am, "loaders") == 0;
+  p.a_mode = (want_loaders && !p.dense_a && p.x_base != nullptr && p.hidden_mult64) ? 1 : 0;
+  if (am != nullptr && strcmp(am, "skip") == 0) p.a_mode = 2;      // timing experiment only
+  if (am != nullptr && strcmp(am, "skiptma") == 0) p.a_mode = 3;   // timing experiment only
+  p.b_skip = getenv("APS_B_SKIP") != nullptr ? 1 : 0;
+  p.debug = getenv("APS_DEBUG") != nullptr ? atoi(getenv("APS_DEBUG")) : 0;
+  return use_pair_variant() ? launch_hidden_variant<T, MODE, true>(mx, mk, mv, p, stream)
+                            : launch_hidden_variant<T, MODE, false>(mx, mk, mv, p, stream);
 }
 
 struct HiddenArgs {
@@ -544,11 +888,11 @@ int check_hidden_args(const char* op, const HiddenArgs& a) {
   return APS_OK;
 }
 
-int make_maps(const HiddenArgs& a, CUtensorMap* mx, CUtensorMap* mk, CUtensorMap* mv) {
+int make_maps(const HiddenArgs& a, CUtensorMap* mx, CUtensorMap* mk, CUtensorMap* mv, bool dense_x = false) {
   int st;
   const uint64_t hd = (uint64_t)a.heads * a.head_size;
   if ((st = make_map(mx, a.hidden_cache, a.dtype, a.hidden_size, a.num_hidden_rows, a.hidden_row_stride,
-                     kSubRows, "hidden cache")) != APS_OK) return st;
+                     dense_x ? kBM : kSubRows, "hidden cache")) != APS_OK) return st;
   if ((st = make_map(mk, a.w_k, a.dtype, a.hidden_size, hd, a.w_stride, kHeadDim, "W_k")) != APS_OK) return st;
   return make_map(mv, a.w_v, a.dtype, a.hidden_size, hd, a.w_stride, kHeadDim, "W_v");
 }
@@ -596,7 +940,9 @@ extern "C" int aps_hybrid_decode_attention(void* out, const void* query, const v
   p.max_blocks_per_seq = max_blocks_per_seq; p.block_size = block_size;
   p.query_stride = query_stride; p.scale_log2 = scale * 1.4426950408889634f;
   p.b_k = b_k; p.b_v = b_v; p.heads = num_heads; p.k_slabs = (hidden_size + 63) / 64;
+  p.x_base = hidden_cache; p.x_row_bytes = hidden_row_stride * 2; p.x_rows = num_hidden_rows; p.hidden_mult64 = hidden_size % 64 == 0;
   p.status = ws.plan + kPlanStatus;
+  p.stats = getenv("APS_STATS") != nullptr ? reinterpret_cast<unsigned long long*>(ws.plan + kPlanStatsWord) : nullptr;
   st = dtype == APS_BF16 ? launch_hidden<__nv_bfloat16, kModeAttend>(mx, mk, mv, p, cs)
                          : launch_hidden<__half, kModeAttend>(mx, mk, mv, p, cs);
   if (st != APS_OK) return st;
@@ -618,11 +964,15 @@ extern "C" int aps_kv_reprojection(void* kv, const void* x, const int32_t* block
               APS_ERR_MISALIGNED, "kv_reprojection: output must be 16-byte aligned with a 16-byte row stride");
   APS_REQUIRE((n_rows + kBM - 1) / kBM < (1LL << 24), APS_ERR_SHAPE, "kv_reprojection: too many rows");
   CUtensorMap mx, mk, mv;
-  if ((st = make_maps(a, &mx, &mk, &mv)) != APS_OK) return st;
+  const char* dense_env = getenv("APS_DENSE_A");
+  const bool dense = block_ids == nullptr && !(dense_env != nullptr && dense_env[0] == '0');
+  if ((st = make_maps(a, &mx, &mk, &mv, dense)) != APS_OK) return st;
   HiddenParams p{};
+  p.dense_a = dense ? 1 : 0;
   p.kv_out = kv; p.block_ids = block_ids; p.n_rows = n_rows; p.kv_stride = kv_stride;
   p.n_store_tiles = (int)((n_rows + kBM - 1) / kBM);
   p.b_k = b_k; p.b_v = b_v; p.heads = num_heads; p.k_slabs = (hidden_size + 63) / 64;
+  p.x_base = x; p.x_row_bytes = x_row_stride * 2; p.x_rows = num_x_rows; p.hidden_mult64 = hidden_size % 64 == 0;
   p.status = status_word;
   cudaStream_t cs = (cudaStream_t)stream;
   return dtype == APS_BF16 ? launch_hidden<__nv_bfloat16, kModeStore>(mx, mk, mv, p, cs)

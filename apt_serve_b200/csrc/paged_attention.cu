@@ -68,6 +68,7 @@ plan_kernel(int* __restrict__ plan, int* __restrict__ part_offset, int2* __restr
     plan[kPlanHidCounter] = 0;
     plan[kPlanStatus] = 0;
   }
+  if (tid >= kPlanStatsWord && tid < kPlanStatsWord + 16) plan[tid] = 0;  // optional kernel counters
 }
 
 // ---- K/V streaming ---------------------------------------------------------------

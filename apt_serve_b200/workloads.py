@@ -124,6 +124,8 @@ class DecodeWorkload:
     use_hidden: List[bool]
     block_tables: List[List[int]]
     block_tables_4_shared: List[List[int]]
+    prefill: Optional["PrefillWriteWorkload"] = None   # configuration 3 only
+    copy_pairs: Optional[torch.Tensor] = None          # [n, 2] int64 (src, dst) block ids
 
     @property
     def heads(self) -> int:
@@ -159,19 +161,30 @@ class DecodeWorkload:
         kw["kv_cache"] = kv
         kw["hidden_cache"] = kv if alias else self.hidden_cache.to(device)
         kw["meta"] = self.meta.to(device)
+        if self.prefill is not None:
+            pf = self.prefill
+            kw["prefill"] = PrefillWriteWorkload(pf.hidden_states.to(device), pf.key.to(device),
+                                                 pf.value.to(device), pf.meta.to(device),
+                                                 pf.block_tables, pf.prompt_lens, pf.use_hidden)
         return DecodeWorkload(**kw)
 
 
 def make_decode_workload(shape: LayerShape, seq_lens: Sequence[int], use_hidden: Sequence[bool],
                          seed: int, device="cpu", tp_rank: int = 0, tp_size: int = 1,
                          with_shared_cache: bool = False, spare_blocks: int = 8,
-                         kv_from_projection: bool = False) -> DecodeWorkload:
+                         kv_from_projection: bool = False,
+                         prefill: Optional[Tuple[Sequence[int], Sequence[bool]]] = None,
+                         copy_fraction: float = 0.0) -> DecodeWorkload:
     """Allocate and fill one layer's caches, weights and step inputs.
 
     Every rank of a tensor-parallel group calls this with the same ``seed``: the
     full-width tensors are drawn identically and each rank keeps its head slice,
     so the ranks' K/V planes, W_q/W_k/W_v rows and W_o columns are consistent
     (additional_designs/model_executor/layers/aptserve_linear.py:545-569, 764-765).
+
+    ``prefill=(prompt_lens, use_hidden)`` adds configuration 3's prefill part: packed
+    prompt tokens (layer inputs and K/V rows) whose blocks come from the same pool;
+    ``copy_fraction`` adds copy-on-write pairs for that share of the blocks in use.
     """
     assert shape.num_heads % tp_size == 0
     bs, d, e = shape.block_size, shape.head_dim, shape.hidden
@@ -179,11 +192,27 @@ def make_decode_workload(shape: LayerShape, seq_lens: Sequence[int], use_hidden:
     hd_rank = h_rank * d
     rng = np.random.default_rng(seed)
     nb = blocks_needed(seq_lens, use_hidden, bs) + spare_blocks
+    if prefill is not None:
+        nb += blocks_needed(prefill[0], prefill[1], bs)
+    n_copy = 0
+    if copy_fraction > 0:
+        n_copy = max(1, int(round(copy_fraction * (nb - spare_blocks))))
+        nb += n_copy
     pool = BlockPool(nb, rng)
     tables = [pool.table_for(s, bs, h) for s, h in zip(seq_lens, use_hidden)]
     shared_tables = [pool.shared_table_for(s, bs) if h else []
                      for s, h in zip(seq_lens, use_hidden)]
     meta = build_decode_metadata(seq_lens, use_hidden, tables, shared_tables, bs)
+    prefill_tables = None
+    if prefill is not None:
+        prefill_tables = [pool.table_for(s, bs, h) for s, h in zip(prefill[0], prefill[1])]
+    copy_pairs = None
+    if n_copy:
+        # copy-on-write pairs: sources among the blocks in use, destinations fresh blocks
+        used = sorted({b % nb for t in tables for b in t})
+        src = rng.choice(used, size=n_copy, replace=len(used) < n_copy)
+        dst = [pool.allocate() for _ in range(n_copy)]
+        copy_pairs = np.stack([np.asarray(src, dtype=np.int64), np.asarray(dst, dtype=np.int64)], axis=1)
 
     dev = torch.device(device)
     gen = torch.Generator(device=dev)
@@ -267,7 +296,19 @@ def make_decode_workload(shape: LayerShape, seq_lens: Sequence[int], use_hidden:
     if with_shared_cache:
         shared_cache = torch.zeros(2, 2 * nb, bs, h_rank, d, dtype=shape.dtype, device=dev)
 
-    return DecodeWorkload(shape=shape, tp_rank=tp_rank, tp_size=tp_size, num_blocks=nb,
+    prefill_part = None
+    if prefill is not None:
+        p_lens, p_hid = [int(x) for x in prefill[0]], [bool(x) for x in prefill[1]]
+        t = sum(p_lens)
+        pk = randn(t, hd_full, std=kv_std)[:, sl].contiguous().view(t, h_rank, d)
+        pv = randn(t, hd_full, std=kv_std)[:, sl].contiguous().view(t, h_rank, d)
+        prefill_part = PrefillWriteWorkload(
+            hidden_states=randn(t, e), key=pk, value=pv,
+            meta=build_prefill_metadata(p_lens, p_hid, prefill_tables, bs).to(dev),
+            block_tables=prefill_tables, prompt_lens=p_lens, use_hidden=p_hid)
+    copy_t = None if copy_pairs is None else torch.from_numpy(copy_pairs).to(dev)
+
+    return DecodeWorkload(prefill=prefill_part, copy_pairs=copy_t, shape=shape, tp_rank=tp_rank, tp_size=tp_size, num_blocks=nb,
                           kv_cache=kv_cache, hidden_cache=hidden_cache,
                           shared_cache=shared_cache, qkv_weight=qkv_weight, qkv_bias=qkv_bias,
                           o_weight=o_weight, o_bias=o_bias, hidden_states=hidden_states,

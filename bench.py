@@ -164,6 +164,7 @@ class LayerStep:
         new_slot = m.slot_mapping[m.hidden_holder_upd]
         self.kv_new_slots = torch.where(m.cache_type != 0, torch.full_like(new_slot, -1), new_slot)
         self.out = torch.empty_like(w.query)
+        self.prefill_events = None   # (start, stop) recorded around prefill_writes when set
         self.workspace = A.attention_workspace(w.query.device, w.query.shape[0],
                                                m.private_block_tables.shape[1], w.shape.block_size, h, d)
 
@@ -186,8 +187,44 @@ class LayerStep:
         dist.all_reduce(y, group=self.tp_group)
         return y + self.w.o_bias
 
+    def prefill_writes(self):
+        """Configuration 3: cache the packed prompt tokens (K/V rows of K/V-designated
+        prompts, layer-input rows of hidden-designated ones) and copy 5 % of the blocks."""
+        from apt_serve_b200 import mixed_cache_ops, ops
+        from apt_serve_b200.attention import FlashAttentionBackend
+        w, pf = self.w, self.w.prefill
+        pm = pf.meta
+        if not hasattr(self, "_prefill_kv_slots"):
+            slots = torch.full_like(pm.slot_mapping, -1)
+            slots[pm.kv_cache_use_tot] = pm.slot_mapping[pm.kv_cache_use_tot]
+            self._prefill_kv_slots = slots
+        ops.reshape_and_cache_flash(pf.key, pf.value, w.kv_cache[0], w.kv_cache[1],
+                                    self._prefill_kv_slots, "auto")
+        mixed_cache_ops.hidden_to_cache(pf.hidden_states, w.hidden_cache, pm.slot_mapping,
+                                        pm.hidden_cache_use_input, pm.hidden_cache_store_tot)
+        if w.copy_pairs is not None:
+            FlashAttentionBackend.copy_blocks([w.kv_cache], w.copy_pairs)
+
+    def prefill_write_bytes(self):
+        """Algorithmic bytes of prefill_writes: read + write of every payload."""
+        w, pf = self.w, self.w.prefill
+        es = w.shape.es
+        n_kv = pf.meta.kv_cache_use_tot.numel()
+        n_h = pf.meta.hidden_cache_use_input.numel()
+        row_kv = 2 * self.h * self.d * es
+        total = 2 * (n_kv * row_kv + n_h * w.shape.hidden * es)
+        if w.copy_pairs is not None:
+            total += 2 * w.copy_pairs.shape[0] * 2 * w.shape.block_size * self.h * self.d * es
+        return total
+
     def step(self):
         w, m = self.w, self.w.meta
+        if w.prefill is not None:
+            if self.prefill_events is not None:
+                self.prefill_events[0].record()
+            self.prefill_writes()
+            if self.prefill_events is not None:
+                self.prefill_events[1].record()
         self.cache_writes(w.hidden_states, w.new_key, w.new_value, self.kv_new_slots)
         out = self.attention(w.query, m.private_block_tables, m.seq_lens_tensor, m.cache_type)
         if self.tp_group is not None:
@@ -219,7 +256,11 @@ def run_ours(args):
     shape = CONFIG_SHAPES[cfg]
     seed = 1000 + cfg
     lens, hid = draw_decode_batch(cfg, seed, batch=args.batch, hidden_fraction=args.hidden_fraction)
-    w = make_decode_workload(shape, lens, hid, seed, dev, tp_rank=rank, tp_size=tp)
+    extra = {}
+    if cfg == 3:
+        from apt_serve_b200.workloads import draw_prefill_batch
+        extra = {"prefill": draw_prefill_batch(), "copy_fraction": 0.05}
+    w = make_decode_workload(shape, lens, hid, seed, dev, tp_rank=rank, tp_size=tp, **extra)
     work = algorithmic_work(shape, lens, hid, tp)
     B = len(lens)
     st = LayerStep(w, group)
@@ -247,13 +288,16 @@ def run_ours(args):
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     lib = N.lib()
+    ev_pf = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
     e0.record()
     for i in range(K):
+        st.prefill_events = ev_pf[i] if w.prefill is not None else None
         lib.aps_set_profile_events(0, ctypes.c_void_p(ev_kv[i][0].cuda_event), ctypes.c_void_p(ev_kv[i][1].cuda_event))
         lib.aps_set_profile_events(1, ctypes.c_void_p(ev_hid[i][0].cuda_event), ctypes.c_void_p(ev_hid[i][1].cuda_event))
         st.step()
     e1.record()
     barrier()
+    st.prefill_events = None
     lib.aps_set_profile_events(0, None, None)
     lib.aps_set_profile_events(1, None, None)
     clocks = sampler.stop() if rank == 0 else None
@@ -265,6 +309,7 @@ def run_ours(args):
     kv_ms = statistics.mean(a.elapsed_time(b) for a, b in ev_kv)
     hid_ms = statistics.mean(a.elapsed_time(b) for a, b in ev_hid)
     status = st.A.attention_status(st.workspace)
+    pf_ms = statistics.mean(a.elapsed_time(b) for a, b in ev_pf) if w.prefill is not None else None
 
     # ---- end to end through the public API with host buffers ----
     m = w.meta
@@ -351,15 +396,24 @@ def run_ours(args):
         "config": {"workload": f"config {cfg}: {shape.name} layer ({shape.num_heads} heads x {shape.head_dim}, "
                                f"hidden {shape.hidden}), {B} decode requests, {sum(hid)} hidden-cached, "
                                f"T_kv={work['t_kv']} T_hidden={work['t_hidden']} cached tokens per rank view",
-                   "step": "new-token cache writes + hybrid decode attention" + (" + o_proj + all-reduce" if tp > 1 else ""),
+                   "step": ("prefill cache writes + block copies + " if w.prefill is not None else "") +
+                           "new-token cache writes + hybrid decode attention" +
+                           (" + o_proj + all-reduce" if tp > 1 else ""),
                    "parallelism": f"tp{tp}" if tp > 1 else "single GPU",
                    "l2": f"inputs larger than L2: {(work['kv_attention_bytes'] + work['hidden_bytes']) / 1e9:.2f} GB streamed per step",
                    "seed": seed},
         "clocks": clocks,
         "e2e": {"value": round(B / e2e_s, 2), "unit": UNIT, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_s * 1e3, 4)},
-        "gpu_launches": 6 * K,
+        "gpu_launches": (6 + (3 if w.prefill is not None else 0)) * K,
         "roofline": roofline, "roofline_kv_path": roofline_kv,
+        **({"roofline_cache_writes": {
+            "kernels": "reshape_and_cache + hidden_to_cache + copy_blocks (prefill part of config 3)",
+            "bound": "hbm", "bytes_per_step": st.prefill_write_bytes(), "ms_per_step": round(pf_ms, 4),
+            "achieved": round(st.prefill_write_bytes() / (pf_ms * 1e-3) / 1e9, 1), "peak": peaks["hbm_gbs"],
+            "unit": "GB/s", "frac": round(st.prefill_write_bytes() / (pf_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
+            "prefill_tokens": int(w.prefill.meta.num_prefill_tokens),
+            "copied_blocks": 0 if w.copy_pairs is None else int(w.copy_pairs.shape[0])}} if pf_ms else {}),
         "device_status": status,
     }
     if cpu_baseline is not None:
