@@ -170,6 +170,20 @@ __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorM
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y)
       : "memory");
 }
+// Same two copies, with the shared-memory destination and the barrier already given as
+// 32-bit shared addresses.
+__device__ __forceinline__ void tma_load_2d_a(uint32_t smem_dst, const CUtensorMap* map, uint32_t bar,
+                                              int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair_a(uint32_t smem_dst, const CUtensorMap* map,
+                                                   uint32_t bar_cluster_addr, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y) : "memory");
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
@@ -268,6 +282,7 @@ struct HiddenParams {
   int dense_a;                // X rows of a tile are contiguous: map_x has a 128-row box
   int a_mode;                 // 0: hidden rows by TMA boxes, 1: by the loader warps (cp.async)
   int b_skip;                 // timing experiment only: do not load W (results are garbage)
+  int split_issue;            // the boxes of a stage are issued by four producer threads
   int debug;                  // timing experiments only: bit 0 skip epilogue math, bit 1 producer ignores empty
   int hidden_mult64;          // hidden size is a multiple of 64 elements
   const void* x_base;         // first row of the hidden cache / X matrix (a_mode 1)
@@ -467,6 +482,142 @@ __device__ __forceinline__ void epilogue_compute(SmemAux* aux, const HiddenParam
   }
 }
 
+// ---- TMA producer role -----------------------------------------------------------
+// Issuing one tensor copy costs the issuing thread on the order of a hundred cycles
+// whatever the size of the box, and a paged tile needs eight 16-row boxes plus the W
+// boxes per 64-element slab: one thread cannot issue them within the 512 cycles the
+// tensor cores need for the slab.  So the boxes of a stage are split over four producer
+// threads in four warps (different scheduler partitions).  Producer 0 also posts the
+// stage's byte count; every producer waits for the stage to be free on its own.
+//   single CTA: 0: W_k, blocks 0-1   1: W_v, blocks 2-3   2: blocks 4-5   3: blocks 6-7
+//   CTA pair:   0: W half, blocks 0-1   1: blocks 2-3   2: blocks 4-5   3: blocks 6-7
+template <typename T, int MODE, bool PAIR>
+__device__ __forceinline__ void tma_producer(const HiddenParams& p, SmemAux* aux, uint8_t* smem,
+                                             const CUtensorMap& map_x, const CUtensorMap& map_wk,
+                                             const CUtensorMap& map_wv, int prod, int n_tiles,
+                                             int n_units, int n_items, int first, int stride,
+                                             uint32_t rank) {
+  using V = Variant<PAIR>;
+  constexpr int kStages = V::kStages;
+  constexpr int kStageBytes = kABytes + V::kBBytes;
+  volatile int* abort_flag = &aux->abort_flag;
+  const bool leader = rank == 0;
+  const bool loaders = !PAIR && p.a_mode >= 1;   // hidden rows come from the loader warps
+  const bool split = p.split_issue != 0 && !loaders;   // else producer 0 issues everything
+  if (!split && prod != 0) return;
+  uint32_t stage = 0, phase = 0;
+  bool ok = true;
+  long long w_empty = 0, w_issue = 0;
+  const long long p_begin = (p.stats && prod == 0) ? clock64() : 0;
+  for (int i = first; i < n_items && ok; i += stride) {
+    const Item it = item_of(i, n_units, p.heads, p.raster_units, p.raster_heads);
+    const int tile = PAIR ? it.unit * 2 + (int)rank : it.unit;
+    const int n_sub = (loaders || p.a_mode == 3) ? 0 : (tile_valid_rows<MODE>(p, tile, n_tiles) + kSubRows - 1) / kSubRows;
+    int sub_row[kSubsPerTile];
+    tile_sub_rows<MODE>(p, n_sub > 0 ? tile : 0, n_sub, sub_row);
+    // a dense X tile is one 128-row box (rows past the end are zero-filled and still
+    // counted); a paged tile is one 16-row box per cache block in use
+    const bool dense = p.dense_a != 0;
+    uint32_t tx_bytes = (uint32_t)((dense ? (n_sub > 0 ? kABytes : 0) : n_sub * kSubBytes) + V::kBBytes);
+    if (PAIR && leader) {
+      const int peer_sub = p.a_mode == 3 ? 0 : (tile_valid_rows<MODE>(p, tile + 1, n_tiles) + kSubRows - 1) / kSubRows;
+      tx_bytes += (uint32_t)((dense ? (peer_sub > 0 ? kABytes : 0) : peer_sub * kSubBytes) + V::kBBytes);
+    }
+    if (p.b_skip) tx_bytes -= (PAIR && leader ? 2 : 1) * V::kBBytes;
+    // the boxes this producer issues.  With the split, a producer owns two fixed block
+    // slots, so its loop holds at most four copy instructions (a copy instruction that is
+    // predicated off still costs the thread some twenty cycles).
+    const bool do_w0 = !p.b_skip && prod == 0;                         // W_k (single) / this CTA's half (pair)
+    const bool do_w1 = !p.b_skip && !PAIR && prod == (split ? 1 : 0);  // W_v (single)
+    const bool do_dense = dense && prod == 0 && n_sub > 0;
+    const bool post = prod == 0 && (!PAIR || leader);                  // posts the stage's byte count
+    const CUtensorMap* w0_map = PAIR ? (leader ? &map_wk : &map_wv) : &map_wk;
+    const int hrow = it.head * kHeadDim;
+    const uint32_t smem_base = smem_u32(smem);
+    const uint32_t full_base = smem_u32(&aux->full[0]);
+    if (split) {
+      const int j0 = prod * 2;
+      int r0 = 0, r1 = 0;
+#pragma unroll
+      for (int j = 0; j < kSubsPerTile; ++j) { if (j == j0) r0 = sub_row[j]; if (j == j0 + 1) r1 = sub_row[j]; }
+      const bool has0 = !dense && j0 < n_sub, has1 = !dense && j0 + 1 < n_sub;
+      for (int ks = 0; ks < p.k_slabs; ++ks) {
+        const long long t0 = (p.stats && prod == 0) ? clock64() : 0;
+        if (!mbar_wait(&aux->empty[stage], phase ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
+        const long long t1 = (p.stats && prod == 0) ? clock64() : 0;
+        const uint32_t a_dst = smem_base + stage * kStageBytes;
+        const uint32_t b_dst = a_dst + kABytes;
+        const uint32_t bar_local = full_base + stage * 8;
+        const int x = ks * (kBKBytes / (int)sizeof(T));
+        if (post) mbar_expect_tx(&aux->full[stage], tx_bytes);
+        if (PAIR) {
+          const uint32_t bar = mapa_u32(bar_local, 0);   // bytes of both CTAs count on the even CTA's barrier
+          if (do_dense) tma_load_2d_pair_a(a_dst, &map_x, bar, x, tile * kBM);
+          if (has0) tma_load_2d_pair_a(a_dst + j0 * kSubBytes, &map_x, bar, x, r0);
+          if (has1) tma_load_2d_pair_a(a_dst + (j0 + 1) * kSubBytes, &map_x, bar, x, r1);
+          if (do_w0) tma_load_2d_pair_a(b_dst, w0_map, bar, x, hrow);
+        } else {
+          if (do_dense) tma_load_2d_a(a_dst, &map_x, bar_local, x, tile * kBM);
+          if (has0) tma_load_2d_a(a_dst + j0 * kSubBytes, &map_x, bar_local, x, r0);
+          if (has1) tma_load_2d_a(a_dst + (j0 + 1) * kSubBytes, &map_x, bar_local, x, r1);
+          if (do_w0) tma_load_2d_a(b_dst, w0_map, bar_local, x, hrow);
+          if (do_w1) tma_load_2d_a(b_dst + V::kBBytes / 2, &map_wv, bar_local, x, hrow);
+        }
+        if (p.stats && prod == 0) { w_empty += t1 - t0; w_issue += clock64() - t1; }
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+      }
+    } else {
+      for (int ks = 0; ks < p.k_slabs; ++ks) {
+        const long long t0 = (p.stats && prod == 0) ? clock64() : 0;
+        if (!mbar_wait(&aux->empty[stage], phase ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
+        const long long t1 = (p.stats && prod == 0) ? clock64() : 0;
+        if (p.debug & 32) {   // experiment: no copy instructions in the loop at all
+          if (post) mbar_expect_tx(&aux->full[stage], 0);
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+          continue;
+        }
+        const uint32_t a_dst = smem_base + stage * kStageBytes;
+        const uint32_t b_dst = a_dst + kABytes;
+        const uint32_t bar_local = full_base + stage * 8;
+        const int x = ks * (kBKBytes / (int)sizeof(T));
+        if (post) mbar_expect_tx(&aux->full[stage], tx_bytes);
+        if (PAIR) {
+          const uint32_t bar = mapa_u32(bar_local, 0);
+          if (do_dense) tma_load_2d_pair_a(a_dst, &map_x, bar, x, tile * kBM);
+          if (!dense) {
+#pragma unroll
+            for (int j = 0; j < kSubsPerTile; ++j)
+              if (j < n_sub) tma_load_2d_pair_a(a_dst + j * kSubBytes, &map_x, bar, x, sub_row[j]);
+          }
+          if (do_w0) tma_load_2d_pair_a(b_dst, w0_map, bar, x, hrow);
+        } else {
+          if (do_dense) tma_load_2d_a(a_dst, &map_x, bar_local, x, tile * kBM);
+          if (!dense) {
+#pragma unroll
+            for (int j = 0; j < kSubsPerTile; ++j)
+              if (j < n_sub) tma_load_2d_a(a_dst + j * kSubBytes, &map_x, bar_local, x, sub_row[j]);
+          }
+          if (do_w0) tma_load_2d_a(b_dst, w0_map, bar_local, x, hrow);
+          if (do_w1) tma_load_2d_a(b_dst + V::kBBytes / 2, &map_wv, bar_local, x, hrow);
+        }
+        if (p.stats && prod == 0) { w_empty += t1 - t0; w_issue += clock64() - t1; }
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+      }
+    }
+  }
+  if (!ok) {
+    // another role gave up: let copies that are still in flight land (bounded)
+    // before the CTA's shared memory is released
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) { }
+  }
+  if (p.stats && prod == 0) {
+    atomicAdd(p.stats + 3, (unsigned long long)w_empty);
+    atomicAdd(p.stats + 4, (unsigned long long)(clock64() - p_begin));
+    atomicAdd(p.stats + 5, (unsigned long long)w_issue);
+  }
+}
+
 // ---- the kernel ---------------------------------------------------------------------
 template <typename T, int MODE, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -519,72 +670,10 @@ hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
   const int stride = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
   if (warp == 0) {
-    // ===================== TMA producer =====================
-    if (lane == 0) {
-      uint32_t stage = 0, phase = 0;
-      bool ok = true;
-      const bool loaders = !PAIR && p.a_mode >= 1;   // hidden rows come from the loader warps
-      long long w_empty = 0;
-      for (int i = first; i < n_items && ok; i += stride) {
-        const Item it = item_of(i, n_units, p.heads, p.raster_units, p.raster_heads);
-        const int tile = PAIR ? it.unit * 2 + (int)rank : it.unit;
-        const int n_sub = (loaders || p.a_mode == 3) ? 0 : (tile_valid_rows<MODE>(p, tile, n_tiles) + kSubRows - 1) / kSubRows;
-        int sub_row[kSubsPerTile];
-        tile_sub_rows<MODE>(p, n_sub > 0 ? tile : 0, n_sub, sub_row);
-        // a dense X tile is one 128-row box (rows past the end are zero-filled and still
-        // counted); a paged tile is one 16-row box per cache block in use
-        const bool dense = p.dense_a != 0;
-        uint32_t tx_bytes = (uint32_t)((dense ? (n_sub > 0 ? kABytes : 0) : n_sub * kSubBytes) + V::kBBytes);
-        if (PAIR && leader) {
-          const int peer_sub = p.a_mode == 3 ? 0 : (tile_valid_rows<MODE>(p, tile + 1, n_tiles) + kSubRows - 1) / kSubRows;
-          tx_bytes += (uint32_t)((dense ? (peer_sub > 0 ? kABytes : 0) : peer_sub * kSubBytes) + V::kBBytes);
-          if (p.b_skip) tx_bytes -= 2 * V::kBBytes;
-        }
-        for (int ks = 0; ks < p.k_slabs; ++ks) {
-          const long long t0 = p.stats ? clock64() : 0;
-          if (!(p.debug & 2) && !mbar_wait(&aux->empty[stage], phase ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
-          if (p.stats) w_empty += clock64() - t0;
-          uint8_t* a_dst = smem + (size_t)stage * kStageBytes;
-          uint8_t* b_dst = a_dst + kABytes;
-          const int x = ks * (kBKBytes / (int)sizeof(T));
-          if (PAIR) {
-            // bytes of both CTAs are counted on the even CTA's barrier
-            if (leader) mbar_expect_tx(&aux->full[stage], tx_bytes);
-            const uint32_t bar = mapa_u32(smem_u32(&aux->full[stage]), 0);
-            if (dense) {
-              if (n_sub > 0) tma_load_2d_pair(a_dst, &map_x, bar, x, tile * kBM);
-            } else {
-#pragma unroll
-              for (int j = 0; j < kSubsPerTile; ++j)
-                if (j < n_sub) tma_load_2d_pair(a_dst + j * kSubBytes, &map_x, bar, x, sub_row[j]);
-            }
-            if (!p.b_skip) tma_load_2d_pair(b_dst, leader ? &map_wk : &map_wv, bar, x, it.head * kHeadDim);
-          } else {
-            if (p.b_skip) { mbar_expect_tx(&aux->full[stage], tx_bytes - V::kBBytes); }
-            else mbar_expect_tx(&aux->full[stage], tx_bytes);
-            if (dense) {
-              if (n_sub > 0) tma_load_2d(a_dst, &map_x, &aux->full[stage], x, tile * kBM);
-            } else {
-#pragma unroll
-              for (int j = 0; j < kSubsPerTile; ++j)
-                if (j < n_sub) tma_load_2d(a_dst + j * kSubBytes, &map_x, &aux->full[stage], x, sub_row[j]);
-            }
-            if (!p.b_skip) {
-              tma_load_2d(b_dst, &map_wk, &aux->full[stage], x, it.head * kHeadDim);
-              tma_load_2d(b_dst + V::kBBytes / 2, &map_wv, &aux->full[stage], x, it.head * kHeadDim);
-            }
-          }
-          if (++stage == kStages) { stage = 0; phase ^= 1; }
-        }
-      }
-      if (!ok) {
-        // another role gave up: let copies that are still in flight land (bounded)
-        // before the CTA's shared memory is released
-        const long long t0 = clock64();
-        while (clock64() - t0 < 2000000LL) { }
-      }
-      if (p.stats) atomicAdd(p.stats + 3, (unsigned long long)w_empty);
-    }
+    // ===================== TMA producer 0 =====================
+    if (lane == 0)
+      tma_producer<T, MODE, PAIR>(p, aux, smem, map_x, map_wk, map_wv, 0, n_tiles, n_units, n_items,
+                                  first, stride, rank);
     __syncwarp();
   } else if (warp == 1) {
     // ===================== MMA issuer (the even CTA of a pair issues for both) =====================
@@ -604,6 +693,10 @@ hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         const uint32_t d_tmem = tmem_base + buf * kBN;
         for (int ks = 0; ks < p.k_slabs; ++ks) {
           t0 = st ? clock64() : 0;
+          if (p.debug & 16) {   // experiment: non-suspending poll
+            uint32_t okk = 0;
+            while (!okk) asm volatile("{.reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0,1,0,p;}" : "=r"(okk) : "r"(smem_u32(&aux->full[stage])), "r"(phase) : "memory");
+          } else
           if (!(p.debug & 4) && !mbar_wait(&aux->full[stage], phase, abort_flag, p.status, 3)) { ok = false; break; }
           if (st) { const long long dt = clock64() - t0; w_full += dt; if (ks == 0) w_first += dt; }
           tc_fence_after();
@@ -657,7 +750,14 @@ hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     // cache block of the tile into the 128-byte-swizzled stage (chunk index XOR row % 8),
     // and the stage's barrier counts one arrival per thread, delivered by the copy unit when
     // that thread's copies have landed.  The W boxes stay on TMA.
-    if (!PAIR && p.a_mode >= 1) {
+    if (!(!PAIR && p.a_mode >= 1)) {
+      // TMA mode: warps 6, 7 and 9 are producers 1..3 (each on its own scheduler partition)
+      const int prod = warp == 6 ? 1 : warp == 7 ? 2 : warp == 9 ? 3 : -1;
+      if (prod > 0 && lane == 0)
+        tma_producer<T, MODE, PAIR>(p, aux, smem, map_x, map_wk, map_wv, prod, n_tiles, n_units, n_items,
+                                    first, stride, rank);
+      __syncwarp();
+    } else {
       const int t = (int)threadIdx.x - (kThreads - kLoaderThreads);
       const int r16 = t >> 3, col = t & 7;
       const uint32_t swz = (uint32_t)(r16 * kBKBytes + ((col ^ (r16 & 7)) << 4));
@@ -731,10 +831,7 @@ hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
       };
       if (p.debug & 1) { release(); epi_barrier(); }
       else epilogue_compute<T, MODE>(aux, p, t_row, tile, tile_ok, it.head, quarter, lane, et, release);
-      if (p.stats && et == 0) {
-        atomicAdd(p.stats + 4, (unsigned long long)(t1 - t0));
-        atomicAdd(p.stats + 5, (unsigned long long)(clock64() - t1));
-      }
+      (void)t0; (void)t1;
     }
   }
 
@@ -861,6 +958,8 @@ int launch_hidden(const CUtensorMap& mx, const CUtensorMap& mk, const CUtensorMa
   if (am != nullptr && strcmp(am, "skiptma") == 0) p.a_mode = 3;   // timing experiment only
   p.b_skip = getenv("APS_B_SKIP") != nullptr ? 1 : 0;
   p.debug = getenv("APS_DEBUG") != nullptr ? atoi(getenv("APS_DEBUG")) : 0;
+  const char* si = getenv("APS_SPLIT_ISSUE");
+  p.split_issue = (si != nullptr && si[0] == '0') ? 0 : 1;
   return use_pair_variant() ? launch_hidden_variant<T, MODE, true>(mx, mk, mv, p, stream)
                             : launch_hidden_variant<T, MODE, false>(mx, mk, mv, p, stream);
 }
