@@ -15,6 +15,7 @@
 #include "aps_common.cuh"
 
 #include <initializer_list>
+#include <stdlib.h>
 
 namespace aps {
 namespace {
@@ -169,8 +170,16 @@ inline int common_vector_bytes(std::initializer_list<uint64_t> values) {
   return v;
 }
 
+// Rows are taken grid-stride by persistent CTAs: at most APS_COPY_CTAS_PER_SM (default 8,
+// i.e. 2048 resident threads) per SM, so that large prefill writes do not pay a CTA launch
+// per 10 KB row.
 inline unsigned grid_for(int64_t rows) {
-  const int64_t cap = 1 << 20;
+  static int per_sm = 0;
+  if (per_sm == 0) {
+    const char* v = getenv("APS_COPY_CTAS_PER_SM");
+    per_sm = v != nullptr && atoi(v) > 0 ? atoi(v) : 8;
+  }
+  const int64_t cap = (int64_t)sm_count() * per_sm;
   return static_cast<unsigned>(rows < cap ? rows : cap);
 }
 

@@ -486,11 +486,10 @@ __device__ __forceinline__ void epilogue_compute(SmemAux* aux, const HiddenParam
 // Issuing one tensor copy costs the issuing thread on the order of a hundred cycles
 // whatever the size of the box, and a paged tile needs eight 16-row boxes plus the W
 // boxes per 64-element slab: one thread cannot issue them within the 512 cycles the
-// tensor cores need for the slab.  So the boxes of a stage are split over four producer
-// threads in four warps (different scheduler partitions).  Producer 0 also posts the
-// stage's byte count; every producer waits for the stage to be free on its own.
-//   single CTA: 0: W_k, blocks 0-1   1: W_v, blocks 2-3   2: blocks 4-5   3: blocks 6-7
-//   CTA pair:   0: W half, blocks 0-1   1: blocks 2-3   2: blocks 4-5   3: blocks 6-7
+// tensor cores need for the slab.  So the boxes of a stage are split over five producer
+// threads in five warps.  Producer 0 (warp 0) posts the stage's byte count and issues the
+// W boxes; producers 1..4 (warps 6..9) issue two cache blocks of the tile each.  Every
+// producer waits for the stage to be free on its own.
 template <typename T, int MODE, bool PAIR>
 __device__ __forceinline__ void tma_producer(const HiddenParams& p, SmemAux* aux, uint8_t* smem,
                                              const CUtensorMap& map_x, const CUtensorMap& map_wk,
@@ -528,7 +527,7 @@ __device__ __forceinline__ void tma_producer(const HiddenParams& p, SmemAux* aux
     // slots, so its loop holds at most four copy instructions (a copy instruction that is
     // predicated off still costs the thread some twenty cycles).
     const bool do_w0 = !p.b_skip && prod == 0;                         // W_k (single) / this CTA's half (pair)
-    const bool do_w1 = !p.b_skip && !PAIR && prod == (split ? 1 : 0);  // W_v (single)
+    const bool do_w1 = !p.b_skip && !PAIR && prod == 0;                // W_v (single)
     const bool do_dense = dense && prod == 0 && n_sub > 0;
     const bool post = prod == 0 && (!PAIR || leader);                  // posts the stage's byte count
     const CUtensorMap* w0_map = PAIR ? (leader ? &map_wk : &map_wv) : &map_wk;
@@ -536,7 +535,7 @@ __device__ __forceinline__ void tma_producer(const HiddenParams& p, SmemAux* aux
     const uint32_t smem_base = smem_u32(smem);
     const uint32_t full_base = smem_u32(&aux->full[0]);
     if (split) {
-      const int j0 = prod * 2;
+      const int j0 = prod > 0 ? (prod - 1) * 2 : kSubsPerTile;   // producer 0 issues the W boxes only
       int r0 = 0, r1 = 0;
 #pragma unroll
       for (int j = 0; j < kSubsPerTile; ++j) { if (j == j0) r0 = sub_row[j]; if (j == j0 + 1) r1 = sub_row[j]; }
@@ -751,8 +750,8 @@ hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     // and the stage's barrier counts one arrival per thread, delivered by the copy unit when
     // that thread's copies have landed.  The W boxes stay on TMA.
     if (!(!PAIR && p.a_mode >= 1)) {
-      // TMA mode: warps 6, 7 and 9 are producers 1..3 (each on its own scheduler partition)
-      const int prod = warp == 6 ? 1 : warp == 7 ? 2 : warp == 9 ? 3 : -1;
+      // TMA mode: warps 6..9 are producers 1..4
+      const int prod = warp - 5;   // warps 6..9 -> producers 1..4
       if (prod > 0 && lane == 0)
         tma_producer<T, MODE, PAIR>(p, aux, smem, map_x, map_wk, map_wv, prod, n_tiles, n_units, n_items,
                                     first, stride, rank);
