@@ -100,4 +100,16 @@ int check_attention_args(const char* op, const void* out, const void* query, con
                          const int32_t* seq_lens, const AttnShape& s, const void* workspace,
                          size_t workspace_bytes, bool need_kv);
 
+// CUDA-core re-projection for the shapes the tensor-core kernel does not take.
+struct SimtHiddenArgs {
+  const void* query; const void* x_base; const void* w_k; const void* b_k; const void* w_v; const void* b_v;
+  const int32_t* block_tables; const int32_t* seq_lens;
+  int max_blocks_per_seq, block_size, heads, head_size, hidden;
+  int64_t query_stride, x_row_stride, w_stride;
+  float scale;
+  int dtype;
+};
+bool hidden_simt_supported(int dtype, int head_size);
+int launch_hidden_simt(const WorkspacePtrs& ws, const SimtHiddenArgs& a, cudaStream_t stream);
+
 }  // namespace aps

@@ -1020,9 +1020,23 @@ extern "C" int aps_hybrid_decode_attention(void* out, const void* query, const v
   APS_REQUIRE(cache_type != nullptr, APS_ERR_NULL_POINTER, "hybrid_decode_attention: cache_type is null");
   HiddenArgs a{hidden_cache, w_k, b_k, w_v, b_v, num_heads, head_size, hidden_size,
                hidden_row_stride, num_hidden_rows, w_stride, dtype};
-  if ((st = check_hidden_args("hybrid_decode_attention", a)) != APS_OK) return st;
+  // fp16 / bf16 with head size 128 run on the tensor cores; fp32 and head sizes 32 / 64 run
+  // the CUDA-core re-projection (same work items, same partials)
+  const bool tensor_path = (dtype == APS_F16 || dtype == APS_BF16) && head_size == kHeadDim &&
+                           getenv("APS_FORCE_SIMT") == nullptr;
   CUtensorMap mx, mk, mv;
-  if ((st = make_maps(a, &mx, &mk, &mv)) != APS_OK) return st;
+  if (tensor_path) {
+    if ((st = check_hidden_args("hybrid_decode_attention", a)) != APS_OK) return st;
+    if ((st = make_maps(a, &mx, &mk, &mv)) != APS_OK) return st;
+  } else {
+    APS_REQUIRE(hidden_simt_supported(dtype, head_size), APS_ERR_UNSUPPORTED,
+                "hybrid_decode_attention: head size %d / dtype %d has no re-projection kernel "
+                "(tensor cores: fp16 or bf16 with head size 128; CUDA cores: head sizes 32, 64, 128)",
+                head_size, dtype);
+    APS_REQUIRE(hidden_cache && w_k && w_v, APS_ERR_NULL_POINTER, "hybrid_decode_attention: null pointer");
+    APS_REQUIRE(hidden_size > 0 && hidden_row_stride >= hidden_size && w_stride >= hidden_size,
+                APS_ERR_SHAPE, "hybrid_decode_attention: bad hidden sizes / strides");
+  }
 
   const WorkspaceLayout w = workspace_layout(batch, max_blocks_per_seq, block_size, num_heads, head_size);
   const WorkspacePtrs ws = workspace_ptrs(workspace, w);
@@ -1030,6 +1044,13 @@ extern "C" int aps_hybrid_decode_attention(void* out, const void* query, const v
   if ((st = launch_plan(ws, seq_lens, cache_type, batch, max_blocks_per_seq, block_size, cs)) != APS_OK) return st;
   if (key_cache != nullptr && value_cache != nullptr) {
     if ((st = launch_kv_attention(ws, query, key_cache, value_cache, block_tables, seq_lens, s, cs)) != APS_OK) return st;
+  }
+  if (!tensor_path) {
+    SimtHiddenArgs sa{query, hidden_cache, w_k, b_k, w_v, b_v, block_tables, seq_lens,
+                      max_blocks_per_seq, block_size, num_heads, head_size, hidden_size,
+                      query_stride, hidden_row_stride, w_stride, scale, dtype};
+    if ((st = launch_hidden_simt(ws, sa, cs)) != APS_OK) return st;
+    return launch_combine(ws, out, seq_lens, s, cs);
   }
   HiddenParams p{};
   p.plan = ws.plan; p.part_offset = ws.part_offset; p.hid_tiles = ws.hid_tiles;

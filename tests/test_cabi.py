@@ -67,11 +67,11 @@ def test_argument_validation_returns_status_codes():
     st = lib.aps_paged_decode_attention(p16, p16 + 2, p16, p16, p16, p16, 4, 4, 2, 64, 16, 128, 128,
                                         16 * 128, 1.0, (p + 255) // 256 * 256, 1 << 30, 1, 0)
     assert st == N.APS_ERR_MISALIGNED
-    # tensor-core path: fp32 / head size 64 are refused with a clear code
+    # a head size no re-projection kernel takes is refused with a clear code
     ws = (p + 255) // 256 * 256
     st = lib.aps_hybrid_decode_attention(p16, p16, p16, p16, p16, p16, 0, p16, 0, p16, p16, p16,
-                                         1, 1, 2, 128, 256, 16, 256, 256, 16 * 256, 256, 64, 256,
-                                         1.0, ws, 1 << 30, 0, 0)
+                                         1, 1, 2, 96, 192, 16, 192, 192, 16 * 192, 192, 64, 192,
+                                         1.0, ws, 1 << 30, 1, 0)
     assert st == N.APS_ERR_UNSUPPORTED
 
 

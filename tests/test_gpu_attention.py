@@ -197,6 +197,47 @@ def test_hybrid_opt66b_bf16_tensor_parallel_slices():
 
 
 # --------------------------------------------------------------------------- #
+# CUDA-core re-projection (fp32, other head sizes)
+# --------------------------------------------------------------------------- #
+def test_config1_full_on_gpu_fp32():
+    """Configuration 1 (OPT-125m layer, fp32, 12 heads x 64, 8 requests): the whole
+    layer-step on the GPU against the CPU oracle; fp32 tolerance 1e-3."""
+    from apt_serve_b200 import mixed_cache_ops, ops
+    w = make_config_workload(1, device="cuda", kv_from_projection=True)
+    cpu = w.cpu()
+    ref = O.decode_layer_step(cpu.hidden_states, cpu.query, cpu.new_key, cpu.new_value, cpu.kv_cache,
+                              cpu.hidden_cache, *cpu.kv_weights(), cpu.meta, cpu.scale)
+    m, h, d = w.meta, w.heads, w.shape.head_dim
+    rows = m.kv_request_rows
+    ops.reshape_and_cache_flash(w.new_key[rows].view(-1, h, d), w.new_value[rows].view(-1, h, d),
+                                w.kv_cache[0], w.kv_cache[1], m.slot_mapping[m.kv_cache_use_tot])
+    mixed_cache_ops.hidden_to_cache(w.hidden_states, w.hidden_cache, m.slot_mapping,
+                                    m.hidden_cache_use_input, m.hidden_cache_store_tot)
+    out = gpu_hybrid(w)
+    assert torch.equal(w.kv_cache.cpu().view(torch.uint8), cpu.kv_cache.view(torch.uint8))
+    assert_close(out, ref, "config 1 on the GPU", 1e-3, 1e-3)
+
+
+@pytest.mark.parametrize("dtype,heads,head_dim", [(torch.float16, 3, 64), (torch.bfloat16, 2, 32),
+                                                  (torch.float32, 2, 128)])
+def test_hybrid_cuda_core_reprojection_shapes(dtype, heads, head_dim):
+    w = small_workload(dtype=dtype, heads=heads, head_dim=head_dim, lens=(5, 40, 17, 129, 200, 16),
+                       hidden=(True, False, True, False, True, True))
+    ref = oracle_out(w)
+    out = gpu_hybrid(w.to("cuda"))
+    tol = 1e-3 if dtype == torch.float32 else 2e-2
+    assert_close(out, ref, f"CUDA-core re-projection {dtype} D{head_dim}", tol, tol)
+
+
+def test_cuda_core_and_tensor_core_reprojection_agree(monkeypatch):
+    w = small_workload(heads=2, head_dim=128, lens=(70, 300, 129), hidden=(True, True, False)).to("cuda")
+    tensor = gpu_hybrid(w).clone()
+    monkeypatch.setenv("APS_FORCE_SIMT", "1")
+    simt = gpu_hybrid(w)
+    assert_close(simt, tensor.float(), "CUDA-core vs tensor-core path", 5e-3, 5e-3)
+
+
+# --------------------------------------------------------------------------- #
 # model-side callers
 # --------------------------------------------------------------------------- #
 def test_opt_attention_fused_matches_literal_and_oracle():
