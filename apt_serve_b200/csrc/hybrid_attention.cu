@@ -934,7 +934,7 @@ int launch_hidden_variant(const CUtensorMap& mx, const CUtensorMap& mk, const CU
 
 // Work-order group sizes: APS_RASTER="units,heads" overrides the default.
 void raster_sizes(int* units, int* heads) {
-  *units = 16; *heads = 8;
+  *units = 8; *heads = 8;
   const char* v = getenv("APS_RASTER");
   if (v != nullptr) {
     int a = 0, b = 0;
