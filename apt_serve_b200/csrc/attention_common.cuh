@@ -15,6 +15,7 @@
 namespace aps {
 
 constexpr int kChunkTokens = 128;
+constexpr int kSubRowsPlan = 16;   // rows of one sub-block of a hidden request's tile list
 
 // Header words at the start of the scratch buffer (device-written).
 enum PlanWord {
@@ -23,13 +24,15 @@ enum PlanWord {
   kPlanKvCounter = 2,     // dynamic work counter of the K/V kernel
   kPlanHidCounter = 3,    // reserved
   kPlanStatus = 4,        // non-zero when a kernel gave up on a bounded wait
+  kPlanNumHidSubs = 5,    // 16-row sub-blocks in the hidden requests' tile list (incl. padding entries)
   kPlanStatsWord = 16,    // 8 x 64-bit cycle counters of the re-projection kernel (debug aid)
   kPlanWords = 64
 };
 
 struct WorkspaceLayout {
   int batch, heads, head_size, max_chunks;  // max_chunks = batch * chunks per longest request
-  size_t off_plan, off_part_offset, off_kv_chunks, off_hid_tiles, off_ml, off_acc, total;
+  size_t off_plan, off_part_offset, off_kv_chunks, off_hid_tiles, off_first_tile, off_hid_subs,
+      off_ml, off_acc, total;
 };
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
@@ -40,13 +43,18 @@ inline WorkspaceLayout workspace_layout(int batch, int max_blocks_per_seq, int b
   w.batch = batch; w.heads = heads; w.head_size = head_size;
   const int64_t max_tokens = (int64_t)max_blocks_per_seq * block_size;
   const int64_t per_req = (max_tokens + kChunkTokens - 1) / kChunkTokens;
-  const int64_t mc = (int64_t)batch * (per_req > 0 ? per_req : 1);
+  // one partial per 128-token chunk; a hidden request whose tiles are packed across requests
+  // can touch one tile more than it has chunks
+  const int64_t mc = (int64_t)batch * ((per_req > 0 ? per_req : 1) + 1);
+  const int64_t subs = (int64_t)batch * (((max_tokens + kSubRowsPlan - 1) / kSubRowsPlan + 7) / 8 * 8) + 8;
   w.max_chunks = (int)mc;
   size_t o = 0;
   w.off_plan = o;        o = align_up(o + kPlanWords * sizeof(int), 256);
   w.off_part_offset = o; o = align_up(o + (size_t)(batch + 1) * sizeof(int), 256);
   w.off_kv_chunks = o;   o = align_up(o + (size_t)mc * sizeof(int2), 256);
   w.off_hid_tiles = o;   o = align_up(o + (size_t)mc * sizeof(int2), 256);
+  w.off_first_tile = o;  o = align_up(o + (size_t)(batch + 1) * sizeof(int), 256);
+  w.off_hid_subs = o;    o = align_up(o + (size_t)subs * sizeof(int2), 256);
   w.off_ml = o;          o = align_up(o + (size_t)mc * heads * 2 * sizeof(float), 256);
   w.off_acc = o;         o = align_up(o + (size_t)mc * heads * head_size * sizeof(float), 256);
   w.total = o;
@@ -57,7 +65,9 @@ struct WorkspacePtrs {
   int* plan;
   int* part_offset;   // [batch + 1] first partial slot of each request
   int2* kv_chunks;    // (request, chunk) of K/V-cached requests, request order
-  int2* hid_tiles;    // (request, chunk) of hidden-cached requests, request order
+  int2* hid_tiles;    // (request, chunk) of hidden-cached requests, request order (unpacked plan only)
+  int* first_tile;    // [batch] first M tile a hidden request has rows in
+  int2* hid_subs;     // per 16-row sub-block of the M tiles: (request, first token) or (-1, 0) padding
   float* part_ml;     // [slot][head][2]
   float* part_acc;    // [slot][head][head_size]
 };
@@ -69,6 +79,8 @@ inline WorkspacePtrs workspace_ptrs(void* base, const WorkspaceLayout& w) {
   p.part_offset = reinterpret_cast<int*>(b + w.off_part_offset);
   p.kv_chunks = reinterpret_cast<int2*>(b + w.off_kv_chunks);
   p.hid_tiles = reinterpret_cast<int2*>(b + w.off_hid_tiles);
+  p.first_tile = reinterpret_cast<int*>(b + w.off_first_tile);
+  p.hid_subs = reinterpret_cast<int2*>(b + w.off_hid_subs);
   p.part_ml = reinterpret_cast<float*>(b + w.off_ml);
   p.part_acc = reinterpret_cast<float*>(b + w.off_acc);
   return p;
@@ -81,9 +93,14 @@ struct AttnShape {
   int dtype;
 };
 
-// cache_type may be NULL (all requests K/V-cached).
+// cache_type may be NULL (all requests K/V-cached).  The M tiles of the hidden requests are
+// described in 16-row sub-blocks (hid_subs, 8 per tile).  pack_tiles = false: every request
+// starts a new tile (tile = 128-token chunk, hid_tiles is filled too); pack_tiles = true:
+// the sub-blocks of consecutive hidden requests are packed back to back, so a tile can hold
+// rows of several requests and only the last tile is partly empty.
 int launch_plan(const WorkspacePtrs& ws, const int32_t* seq_lens, const int32_t* cache_type,
-                int batch, int max_blocks_per_seq, int block_size, cudaStream_t stream);
+                int batch, int max_blocks_per_seq, int block_size, bool pack_tiles,
+                cudaStream_t stream);
 
 int launch_kv_attention(const WorkspacePtrs& ws, const void* query, const void* key_cache,
                         const void* value_cache, const int32_t* block_tables,

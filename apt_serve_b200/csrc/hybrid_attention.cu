@@ -82,12 +82,18 @@ struct SmemAux {
   uint64_t acc_empty[2];
   uint32_t tmem_base;
   int abort_flag;
-  float q[kHeadDim];
+  // epilogue scratch.  A tile can hold rows of several requests: a SEGMENT is a run of
+  // sub-blocks of one request; everything below is kept per sub-block or per segment.
+  int2 sub_rec[kSubsPerTile];          // (request, first token) of each sub-block, (-1, 0) = none
+  int sub_seg[kSubsPerTile];           // segment of each sub-block, -1 = none
+  int seg_req[kSubsPerTile];           // request of each segment
+  int n_seg;
+  alignas(16) float q[kSubsPerTile][kHeadDim];   // per segment: query row of its request, pre-scaled
   float bk[kHeadDim];
   float bv[kHeadDim];
-  float red_max[4];
-  float red_sum[4];
-  float red_acc[4][kHeadDim];
+  float sub_max[kSubsPerTile];
+  float sub_sum[kSubsPerTile];
+  alignas(16) float red_acc[kSubsPerTile][kHeadDim];   // written as float2
 };
 
 template <bool PAIR>
@@ -256,7 +262,8 @@ struct HiddenParams {
   // attend mode
   int* plan;
   const int* part_offset;
-  const int2* hid_tiles;
+  const int2* hid_subs;       // per 16-row sub-block of the M tiles: (request, first token) / (-1, 0)
+  const int* first_tile;      // [batch] first M tile a hidden request has rows in
   float* part_ml;
   float* part_acc;
   const void* query;
@@ -315,29 +322,37 @@ __device__ __forceinline__ Item item_of(int i, int n_units, int heads, int ru, i
   return it;
 }
 
-// Valid rows of M tile `tile` (0 when the tile does not exist).
+// Number of 16-row sub-blocks of M tile `tile` that hold rows (they are always the leading
+// ones; 0 when the tile does not exist).
 template <int MODE>
-__device__ __forceinline__ int tile_valid_rows(const HiddenParams& p, int tile, int n_tiles) {
+__device__ __forceinline__ int tile_n_sub(const HiddenParams& p, int tile, int n_tiles) {
   if (tile >= n_tiles) return 0;
   if (MODE == kModeAttend) {
-    const int2 rc = p.hid_tiles[tile];
-    const int seq = min(p.seq_lens[rc.x], p.max_blocks_per_seq * p.block_size);
-    return min(kBM, seq - rc.y * kBM);
+    const int4* rec = reinterpret_cast<const int4*>(p.hid_subs + (int64_t)tile * kSubsPerTile);
+    int n = 0;
+#pragma unroll
+    for (int j = 0; j < kSubsPerTile / 2; ++j) {
+      const int4 r = rec[j];   // two (request, first token) records
+      n += (r.x >= 0) + (r.z >= 0);
+    }
+    return n;
   }
-  return (int)min((int64_t)kBM, p.n_rows - (int64_t)tile * kBM);
+  const int valid = (int)min((int64_t)kBM, p.n_rows - (int64_t)tile * kBM);
+  return (valid + kSubRows - 1) / kSubRows;
 }
 
-// First hidden-cache row of each 16-row sub-block of a tile.
+// First hidden-cache row of each of the tile's leading n_sub sub-blocks.
 template <int MODE>
 __device__ __forceinline__ void tile_sub_rows(const HiddenParams& p, int tile, int n_sub, int* sub_row) {
   if (MODE == kModeAttend) {
-    const int2 rc = p.hid_tiles[tile < 0 ? 0 : tile];
-    const int32_t* bt = p.block_tables + (int64_t)rc.x * p.max_blocks_per_seq;
-    const int tok0 = rc.y * kBM;
 #pragma unroll
     for (int j = 0; j < kSubsPerTile; ++j) {
-      const int tok = tok0 + j * kSubRows;
-      sub_row[j] = j < n_sub ? bt[tok / p.block_size] * p.block_size + tok % p.block_size : 0;
+      sub_row[j] = 0;
+      if (j < n_sub) {
+        const int2 rec = p.hid_subs[(int64_t)tile * kSubsPerTile + j];   // (request, first token)
+        const int32_t* bt = p.block_tables + (int64_t)rec.x * p.max_blocks_per_seq;
+        sub_row[j] = bt[rec.y / p.block_size] * p.block_size + rec.y % p.block_size;
+      }
     }
   } else {
 #pragma unroll
@@ -351,41 +366,54 @@ __device__ __forceinline__ void tile_sub_rows(const HiddenParams& p, int tile, i
   }
 }
 
-// Butterfly column sum: on return v[0] of lane L holds the sum over the warp's
-// 32 lanes of their v[L].
-__device__ __forceinline__ void warp_column_sum(float* v, int lane) {
+// Column sum inside each 16-lane half of the warp: on return v[0], v[1] of a lane hold,
+// for columns 2*(lane%16) and 2*(lane%16)+1, the sum over the 16 lanes of its half.
+__device__ __forceinline__ void half_warp_column_sum(float* v, int lane) {
 #pragma unroll
-  for (int step = 0; step < 5; ++step) {
-    const int off = 16 >> step;
+  for (int step = 0; step < 4; ++step) {
+    const int off = 8 >> step, half = 16 >> step;
     const bool upper = (lane & off) != 0;
 #pragma unroll
-    for (int i = 0; i < off; ++i) {
-      const float send = upper ? v[i] : v[i + off];
-      const float keep = upper ? v[i + off] : v[i];
+    for (int i = 0; i < half; ++i) {
+      const float send = upper ? v[i] : v[i + half];
+      const float keep = upper ? v[i + half] : v[i];
       v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
     }
   }
 }
 
 // ---- epilogue (the 128 threads of warps 2..5) --------------------------------------
-// Before the accumulator is ready: stage q (attend mode) and the biases of head `head`.
+// Before the accumulator is ready: find the tile's segments, stage the query row of every
+// segment's request (attend mode) and the biases of head `head`.
 template <typename T, int MODE>
 __device__ __forceinline__ void epilogue_stage_inputs(SmemAux* aux, const HiddenParams& p, int tile,
                                                       bool tile_ok, int head, int et) {
   const int hcol = head * kHeadDim;
   const T* bk = static_cast<const T*>(p.b_k);
   const T* bv = static_cast<const T*>(p.b_v);
-  if (MODE == kModeAttend) {
-    float qv = 0.f;
-    if (tile_ok) {
-      const int req = p.hid_tiles[tile].x;
-      const T* q = static_cast<const T*>(p.query) + req * p.query_stride + hcol;
-      qv = Elem<T>::to_float(q[et]) * p.scale_log2;
-    }
-    aux->q[et] = qv;
-  }
   aux->bk[et] = bk ? Elem<T>::to_float(bk[hcol + et]) : 0.f;
   aux->bv[et] = bv ? Elem<T>::to_float(bv[hcol + et]) : 0.f;
+  if (MODE == kModeAttend) {
+    if (et < kSubsPerTile)
+      aux->sub_rec[et] = tile_ok ? p.hid_subs[(int64_t)tile * kSubsPerTile + et] : make_int2(-1, 0);
+    epi_barrier();
+    if (et == 0) {
+      int n = 0;
+      for (int j = 0; j < kSubsPerTile; ++j) {
+        const int r = aux->sub_rec[j].x;
+        if (r < 0) { aux->sub_seg[j] = -1; continue; }
+        if (n == 0 || aux->seg_req[n - 1] != r || aux->sub_seg[j - 1] < 0) aux->seg_req[n++] = r;
+        aux->sub_seg[j] = n - 1;
+      }
+      aux->n_seg = n;
+    }
+    epi_barrier();
+    const int n_seg = aux->n_seg;
+    for (int sgm = 0; sgm < n_seg; ++sgm) {
+      const T* q = static_cast<const T*>(p.query) + aux->seg_req[sgm] * p.query_stride + hcol;
+      aux->q[sgm][et] = Elem<T>::to_float(q[et]) * p.scale_log2;
+    }
+  }
   epi_barrier();
 }
 
@@ -426,14 +454,16 @@ __device__ __forceinline__ void epilogue_compute(SmemAux* aux, const HiddenParam
     return;
   }
 
-  int req = 0, chunk = 0;
+  // this thread's row: sub-block `sub` of the tile, row `row % 16` of it
+  const int sub = row >> 4;
+  const int2 rec = aux->sub_rec[sub];
+  const int my_seg = aux->sub_seg[sub];
   bool valid = false;
-  if (tile_ok) {
-    const int2 rc = p.hid_tiles[tile];
-    req = rc.x; chunk = rc.y;
-    const int seq = min(p.seq_lens[req], p.max_blocks_per_seq * p.block_size);
-    valid = chunk * kBM + row < seq;
+  if (my_seg >= 0) {
+    const int seq = min(p.seq_lens[rec.x], p.max_blocks_per_seq * p.block_size);
+    valid = rec.y + (row & 15) < seq;
   }
+  const float* qs = aux->q[my_seg >= 0 ? my_seg : 0];
   // ---- scores: s = q . (K_row + b_k), already in the log2 domain ----
   float s = 0.f;
 #pragma unroll 1
@@ -442,22 +472,26 @@ __device__ __forceinline__ void epilogue_compute(SmemAux* aux, const HiddenParam
     tmem_ld_wait();
 #pragma unroll
     for (int j = 0; j < 32; ++j)
-      s = fmaf(aux->q[c * 32 + j], __uint_as_float(r[j]) + aux->bk[c * 32 + j], s);
+      s = fmaf(qs[c * 32 + j], __uint_as_float(r[j]) + aux->bk[c * 32 + j], s);
   }
   s = valid ? s : -INFINITY;
-  float wm = s;
+  // max over the 16 rows of the sub-block, then over the sub-blocks of the segment
+  float hm = s;
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, o));
-  if (lane == 0) aux->red_max[quarter] = wm;
+  for (int o = 8; o > 0; o >>= 1) hm = fmaxf(hm, __shfl_xor_sync(0xffffffffu, hm, o));
+  if ((lane & 15) == 0) aux->sub_max[sub] = hm;
   epi_barrier();
-  const float mx = fmaxf(fmaxf(aux->red_max[0], aux->red_max[1]), fmaxf(aux->red_max[2], aux->red_max[3]));
-  const float pr = valid ? exp2f(s - mx) : 0.f;
-  float ws = pr;
+  float mx = -INFINITY;
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) ws += __shfl_xor_sync(0xffffffffu, ws, o);
-  if (lane == 0) aux->red_sum[quarter] = ws;
+  for (int j = 0; j < kSubsPerTile; ++j)
+    if (aux->sub_seg[j] == my_seg) mx = fmaxf(mx, aux->sub_max[j]);
+  const float pr = valid ? exp2f(s - mx) : 0.f;
+  float hs = pr;
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) hs += __shfl_xor_sync(0xffffffffu, hs, o);
+  if ((lane & 15) == 0) aux->sub_sum[sub] = hs;
 
-  // ---- weighted V rows, column sums over the warp's 32 rows ----
+  // ---- weighted V rows, column sums over the 16 rows of the sub-block ----
 #pragma unroll 1
   for (int c = 0; c < 4; ++c) {
     tmem_ld32(t_row + kHeadDim + c * 32, r);
@@ -466,20 +500,28 @@ __device__ __forceinline__ void epilogue_compute(SmemAux* aux, const HiddenParam
 #pragma unroll
     for (int j = 0; j < 32; ++j)
       v[j] = valid ? pr * (__uint_as_float(r[j]) + aux->bv[c * 32 + j]) : 0.f;
-    warp_column_sum(v, lane);
-    aux->red_acc[quarter][c * 32 + lane] = v[0];
+    half_warp_column_sum(v, lane);
+    *reinterpret_cast<float2*>(&aux->red_acc[sub][c * 32 + 2 * (lane & 15)]) = make_float2(v[0], v[1]);
   }
   release();
   epi_barrier();
-  if (tile_ok) {
-    const float a = aux->red_acc[0][et] + aux->red_acc[1][et] + aux->red_acc[2][et] + aux->red_acc[3][et];
-    const int64_t slot = (int64_t)(p.part_offset[req] + chunk) * p.heads + head;
+  // ---- one partial per segment: thread et owns column et ----
+  const int n_seg = aux->n_seg;
+  for (int sgm = 0; sgm < n_seg; ++sgm) {
+    float a = 0.f, m_seg = -INFINITY, l_seg = 0.f;
+#pragma unroll
+    for (int j = 0; j < kSubsPerTile; ++j)
+      if (aux->sub_seg[j] == sgm) {
+        a += aux->red_acc[j][et];
+        m_seg = fmaxf(m_seg, aux->sub_max[j]);
+        l_seg += aux->sub_sum[j];
+      }
+    const int req = aux->seg_req[sgm];
+    const int64_t slot = (int64_t)(p.part_offset[req] + tile - p.first_tile[req]) * p.heads + head;
     p.part_acc[slot * kHeadDim + et] = a;
-    if (et == 0) {
-      const float l = aux->red_sum[0] + aux->red_sum[1] + aux->red_sum[2] + aux->red_sum[3];
-      *reinterpret_cast<float2*>(p.part_ml + slot * 2) = make_float2(mx, l);
-    }
+    if (et == 0) *reinterpret_cast<float2*>(p.part_ml + slot * 2) = make_float2(m_seg, l_seg);
   }
+  epi_barrier();  // the segment tables and reduction buffers are rewritten by the next item
 }
 
 // ---- TMA producer role -----------------------------------------------------------
@@ -511,7 +553,7 @@ __device__ __forceinline__ void tma_producer(const HiddenParams& p, SmemAux* aux
   for (int i = first; i < n_items && ok; i += stride) {
     const Item it = item_of(i, n_units, p.heads, p.raster_units, p.raster_heads);
     const int tile = PAIR ? it.unit * 2 + (int)rank : it.unit;
-    const int n_sub = (loaders || p.a_mode == 3) ? 0 : (tile_valid_rows<MODE>(p, tile, n_tiles) + kSubRows - 1) / kSubRows;
+    const int n_sub = (loaders || p.a_mode == 3) ? 0 : tile_n_sub<MODE>(p, tile, n_tiles);
     int sub_row[kSubsPerTile];
     tile_sub_rows<MODE>(p, n_sub > 0 ? tile : 0, n_sub, sub_row);
     // a dense X tile is one 128-row box (rows past the end are zero-filled and still
@@ -519,7 +561,7 @@ __device__ __forceinline__ void tma_producer(const HiddenParams& p, SmemAux* aux
     const bool dense = p.dense_a != 0;
     uint32_t tx_bytes = (uint32_t)((dense ? (n_sub > 0 ? kABytes : 0) : n_sub * kSubBytes) + V::kBBytes);
     if (PAIR && leader) {
-      const int peer_sub = p.a_mode == 3 ? 0 : (tile_valid_rows<MODE>(p, tile + 1, n_tiles) + kSubRows - 1) / kSubRows;
+      const int peer_sub = p.a_mode == 3 ? 0 : tile_n_sub<MODE>(p, tile + 1, n_tiles);
       tx_bytes += (uint32_t)((dense ? (peer_sub > 0 ? kABytes : 0) : peer_sub * kSubBytes) + V::kBBytes);
     }
     if (p.b_skip) tx_bytes -= (PAIR && leader ? 2 : 1) * V::kBBytes;
@@ -766,7 +808,7 @@ hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
       for (int i = first; i < n_items && ok; i += stride) {
         const Item it = item_of(i, n_units, p.heads, p.raster_units, p.raster_heads);
         const int tile = it.unit;
-        const int n_sub = (tile_valid_rows<MODE>(p, tile, n_tiles) + kSubRows - 1) / kSubRows;
+        const int n_sub = tile_n_sub<MODE>(p, tile, n_tiles);
         int sub_row[kSubsPerTile];
         tile_sub_rows<MODE>(p, n_sub > 0 ? tile : 0, n_sub, sub_row);
         const char* src[kSubsPerTile];
@@ -1041,7 +1083,11 @@ extern "C" int aps_hybrid_decode_attention(void* out, const void* query, const v
   const WorkspaceLayout w = workspace_layout(batch, max_blocks_per_seq, block_size, num_heads, head_size);
   const WorkspacePtrs ws = workspace_ptrs(workspace, w);
   cudaStream_t cs = (cudaStream_t)stream;
-  if ((st = launch_plan(ws, seq_lens, cache_type, batch, max_blocks_per_seq, block_size, cs)) != APS_OK) return st;
+  // the tensor-core kernel takes M tiles packed across requests; APS_PACK_TILES=0 starts a new
+  // tile per request (what the CUDA-core kernel needs)
+  const char* pk = getenv("APS_PACK_TILES");
+  const bool pack_tiles = tensor_path && !(pk != nullptr && pk[0] == '0');
+  if ((st = launch_plan(ws, seq_lens, cache_type, batch, max_blocks_per_seq, block_size, pack_tiles, cs)) != APS_OK) return st;
   if (key_cache != nullptr && value_cache != nullptr) {
     if ((st = launch_kv_attention(ws, query, key_cache, value_cache, block_tables, seq_lens, s, cs)) != APS_OK) return st;
   }
@@ -1053,7 +1099,7 @@ extern "C" int aps_hybrid_decode_attention(void* out, const void* query, const v
     return launch_combine(ws, out, seq_lens, s, cs);
   }
   HiddenParams p{};
-  p.plan = ws.plan; p.part_offset = ws.part_offset; p.hid_tiles = ws.hid_tiles;
+  p.plan = ws.plan; p.part_offset = ws.part_offset; p.hid_subs = ws.hid_subs; p.first_tile = ws.first_tile;
   p.part_ml = ws.part_ml; p.part_acc = ws.part_acc; p.query = query;
   p.block_tables = block_tables; p.seq_lens = seq_lens;
   p.max_blocks_per_seq = max_blocks_per_seq; p.block_size = block_size;

@@ -24,49 +24,98 @@ constexpr int kKvWarps = 8;
 constexpr unsigned kFull = 0xffffffffu;
 
 // ---- planning ------------------------------------------------------------------
+// One CTA.  Thread t handles a contiguous run of requests; two block-wide prefix sums:
+// first over (K/V chunks, hidden sub-blocks), which fixes where each hidden request's rows
+// sit in the tile list, then over the number of softmax partials each request will leave.
+__device__ __forceinline__ void block_scan2(int* sa, int* sb, int tid, int& a, int& b) {
+  sa[tid] = a; sb[tid] = b;
+  __syncthreads();
+  for (int off = 1; off < kPlanThreads; off <<= 1) {
+    int x = 0, y = 0;
+    if (tid >= off) { x = sa[tid - off]; y = sb[tid - off]; }
+    __syncthreads();
+    sa[tid] += x; sb[tid] += y;
+    __syncthreads();
+  }
+  a = sa[tid]; b = sb[tid];   // inclusive sums
+}
+
 __global__ void __launch_bounds__(kPlanThreads)
 plan_kernel(int* __restrict__ plan, int* __restrict__ part_offset, int2* __restrict__ kv_chunks,
-            int2* __restrict__ hid_tiles, const int32_t* __restrict__ seq_lens,
-            const int32_t* __restrict__ cache_type, int batch, int max_tokens) {
-  __shared__ int s_tot[kPlanThreads], s_kv[kPlanThreads], s_hid[kPlanThreads];
+            int2* __restrict__ hid_tiles, int* __restrict__ first_tile, int2* __restrict__ hid_subs,
+            const int32_t* __restrict__ seq_lens, const int32_t* __restrict__ cache_type, int batch,
+            int max_tokens, int pack_tiles) {
+  __shared__ int sa[kPlanThreads], sb[kPlanThreads];
   const int tid = threadIdx.x;
   const int per = (batch + kPlanThreads - 1) / kPlanThreads;
   const int r0 = min(batch, tid * per), r1 = min(batch, r0 + per);
-  int tot = 0, kv = 0, hid = 0;
+  auto seq_of = [&](int r) { return max(0, min(seq_lens[r], max_tokens)); };
+  auto hidden = [&](int r) { return cache_type != nullptr && cache_type[r] != 0; };
+  auto subs_of = [&](int s) {   // sub-blocks a hidden request of s tokens occupies in the tile list
+    const int n = (s + kSubRowsPlan - 1) / kSubRowsPlan;
+    return pack_tiles ? n : (n + 7) / 8 * 8;
+  };
+  // pass 1: K/V chunks and hidden sub-blocks
+  int kv = 0, sub = 0;
   for (int r = r0; r < r1; ++r) {
-    const int s = max(0, min(seq_lens[r], max_tokens));
-    const int c = (s + kChunkTokens - 1) / kChunkTokens;
-    tot += c;
-    if (cache_type != nullptr && cache_type[r] != 0) hid += c; else kv += c;
+    const int s = seq_of(r);
+    if (hidden(r)) sub += subs_of(s); else kv += (s + kChunkTokens - 1) / kChunkTokens;
   }
-  s_tot[tid] = tot; s_kv[tid] = kv; s_hid[tid] = hid;
+  int kv_inc = kv, sub_inc = sub;
+  block_scan2(sa, sb, tid, kv_inc, sub_inc);
+  const int total_kv = sa[kPlanThreads - 1], total_sub = sb[kPlanThreads - 1];
   __syncthreads();
-  for (int off = 1; off < kPlanThreads; off <<= 1) {
-    int a = 0, b = 0, c = 0;
-    if (tid >= off) { a = s_tot[tid - off]; b = s_kv[tid - off]; c = s_hid[tid - off]; }
-    __syncthreads();
-    s_tot[tid] += a; s_kv[tid] += b; s_hid[tid] += c;
-    __syncthreads();
-  }
-  int o_tot = s_tot[tid] - tot, o_kv = s_kv[tid] - kv, o_hid = s_hid[tid] - hid;
-  for (int r = r0; r < r1; ++r) {
-    const int s = max(0, min(seq_lens[r], max_tokens));
-    const int c = (s + kChunkTokens - 1) / kChunkTokens;
-    part_offset[r] = o_tot;
-    const bool is_hid = cache_type != nullptr && cache_type[r] != 0;
-    for (int j = 0; j < c; ++j) {
-      if (is_hid) hid_tiles[o_hid++] = make_int2(r, j);
-      else kv_chunks[o_kv++] = make_int2(r, j);
+  int o_kv = kv_inc - kv, o_sub = sub_inc - sub;
+  // pass 2: partial slots per request (K/V: one per chunk; hidden: one per tile it has rows in)
+  int slots = 0, dummy = 0;
+  {
+    int g = o_sub;
+    for (int r = r0; r < r1; ++r) {
+      const int s = seq_of(r);
+      if (hidden(r)) {
+        const int n = subs_of(s), real = (s + kSubRowsPlan - 1) / kSubRowsPlan;
+        if (real > 0) slots += (g + real - 1) / 8 - g / 8 + 1;
+        g += n;
+      } else {
+        slots += (s + kChunkTokens - 1) / kChunkTokens;
+      }
     }
-    o_tot += c;
+  }
+  int slots_inc = slots;
+  block_scan2(sa, sb, tid, slots_inc, dummy);
+  const int total_slots = sa[kPlanThreads - 1];
+  int o_slot = slots_inc - slots;
+  // write-out
+  int g = o_sub;
+  for (int r = r0; r < r1; ++r) {
+    const int s = seq_of(r);
+    part_offset[r] = o_slot;
+    if (hidden(r)) {
+      const int n = subs_of(s), real = (s + kSubRowsPlan - 1) / kSubRowsPlan;
+      first_tile[r] = g / 8;
+      for (int j = 0; j < n; ++j)
+        hid_subs[g + j] = j < real ? make_int2(r, j * kSubRowsPlan) : make_int2(-1, 0);
+      if (!pack_tiles)
+        for (int c = 0; c < n / 8; ++c) hid_tiles[g / 8 + c] = make_int2(r, c);
+      if (real > 0) o_slot += (g + real - 1) / 8 - g / 8 + 1;
+      g += n;
+    } else {
+      first_tile[r] = 0;
+      const int c = (s + kChunkTokens - 1) / kChunkTokens;
+      for (int j = 0; j < c; ++j) kv_chunks[o_kv++] = make_int2(r, j);
+      o_slot += c;
+    }
   }
   if (tid == kPlanThreads - 1) {
-    part_offset[batch] = s_tot[tid];
-    plan[kPlanNumKvChunks] = s_kv[tid];
-    plan[kPlanNumHidTiles] = s_hid[tid];
+    part_offset[batch] = total_slots;
+    plan[kPlanNumKvChunks] = total_kv;
+    plan[kPlanNumHidTiles] = (total_sub + 7) / 8;
+    plan[kPlanNumHidSubs] = total_sub;
     plan[kPlanKvCounter] = 0;
     plan[kPlanHidCounter] = 0;
     plan[kPlanStatus] = 0;
+    // entries between the last sub-block and the end of the last tile read as padding
+    for (int j = total_sub; j < (total_sub + 7) / 8 * 8; ++j) hid_subs[j] = make_int2(-1, 0);
   }
   if (tid >= kPlanStatsWord && tid < kPlanStatsWord + 16) plan[tid] = 0;  // optional kernel counters
 }
@@ -273,10 +322,11 @@ bool kv_attention_supported(int dtype, int head_size) {
 }
 
 int launch_plan(const WorkspacePtrs& ws, const int32_t* seq_lens, const int32_t* cache_type,
-                int batch, int max_blocks_per_seq, int block_size, cudaStream_t stream) {
+                int batch, int max_blocks_per_seq, int block_size, bool pack_tiles,
+                cudaStream_t stream) {
   plan_kernel<<<1, kPlanThreads, 0, stream>>>(ws.plan, ws.part_offset, ws.kv_chunks, ws.hid_tiles,
-                                              seq_lens, cache_type, batch,
-                                              max_blocks_per_seq * block_size);
+                                              ws.first_tile, ws.hid_subs, seq_lens, cache_type, batch,
+                                              max_blocks_per_seq * block_size, pack_tiles ? 1 : 0);
   return launch_status("plan_kernel");
 }
 
@@ -372,7 +422,7 @@ extern "C" int aps_paged_decode_attention(void* out, const void* query, const vo
   const WorkspaceLayout w = workspace_layout(batch, max_blocks_per_seq, block_size, num_heads, head_size);
   const WorkspacePtrs ws = workspace_ptrs(workspace, w);
   cudaStream_t cs = (cudaStream_t)stream;
-  if ((st = launch_plan(ws, seq_lens, nullptr, batch, max_blocks_per_seq, block_size, cs)) != APS_OK) return st;
+  if ((st = launch_plan(ws, seq_lens, nullptr, batch, max_blocks_per_seq, block_size, false, cs)) != APS_OK) return st;
   if ((st = launch_kv_attention(ws, query, key_cache, value_cache, block_tables, seq_lens, s, cs)) != APS_OK) return st;
   return launch_combine(ws, out, seq_lens, s, cs);
 }
@@ -448,7 +498,7 @@ extern "C" int aps_paged_decode_attention_static(void* out, const void* query, c
   // plan_kernel rewrites every word of the scratch header (work counter, status word,
   // list sizes) and every partial that the combine reads is rewritten by this call, so
   // nothing left over from the previous call is ever read
-  if ((st = launch_plan(ws, seq_lens, nullptr, batch, max_blocks_per_seq, block_size, cs)) != APS_OK) return st;
+  if ((st = launch_plan(ws, seq_lens, nullptr, batch, max_blocks_per_seq, block_size, false, cs)) != APS_OK) return st;
   if ((st = launch_kv_attention(ws, query, key_cache, value_cache, block_tables, seq_lens, s, cs)) != APS_OK) return st;
   return launch_combine(ws, out, seq_lens, s, cs);
 }

@@ -157,8 +157,9 @@ def test_hybrid_opt13b_shapes_reduced_batch():
 
 def test_hybrid_full_config2_subset_oracle_and_permutation_invariance():
     """Full config 2 (256 requests): a seeded subset of requests is checked against
-    the oracle; the whole batch is checked by a size-independent property:
-    reversing the request order permutes the output rows."""
+    the oracle; the whole batch is checked by size-independent properties:
+    reversing the request order permutes the output rows, and a repeated call
+    returns the same bits."""
     w = make_config_workload(2, device="cuda")
     out = gpu_hybrid(w)
     assert torch.isfinite(out.float()).all()
@@ -175,7 +176,10 @@ def test_hybrid_full_config2_subset_oracle_and_permutation_invariance():
                                      wv, bv, w.meta.private_block_tables[perm].contiguous(),
                                      w.meta.seq_lens_tensor[perm].contiguous(),
                                      w.meta.cache_type[perm].contiguous(), w.scale)
-    assert torch.equal(out2, out[perm])
+    # M tiles are packed across requests, so the order changes which rows share a partial:
+    # the permuted result agrees to rounding, and a given order is reproducible bit for bit
+    assert_close(out2, out[perm].float(), "request permutation", 2e-3, 2e-3)
+    assert torch.equal(gpu_hybrid(w), out)
 
 
 def test_hybrid_opt66b_bf16_tensor_parallel_slices():
