@@ -1005,6 +1005,25 @@ int launch_hidden(const CUtensorMap& mx, const CUtensorMap& mk, const CUtensorMa
                             : launch_hidden_variant<T, MODE, false>(mx, mk, mv, p, stream);
 }
 
+// Per-device side stream and fork / join events, created on first use, kept until exit.
+struct SideStream { cudaStream_t stream; cudaEvent_t forked, joined; };
+int side_stream(SideStream** out) {
+  static SideStream table[64] = {};
+  int dev = 0;
+  APS_CUDA(cudaGetDevice(&dev));
+  APS_REQUIRE(dev >= 0 && dev < 64, APS_ERR_CUDA, "device index %d out of range", dev);
+  SideStream* s = &table[dev];
+  if (s->stream == nullptr) {
+    cudaStream_t st;
+    APS_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+    APS_CUDA(cudaEventCreateWithFlags(&s->forked, cudaEventDisableTiming));
+    APS_CUDA(cudaEventCreateWithFlags(&s->joined, cudaEventDisableTiming));
+    s->stream = st;
+  }
+  *out = s;
+  return APS_OK;
+}
+
 struct HiddenArgs {
   const void* hidden_cache; const void* w_k; const void* b_k; const void* w_v; const void* b_v;
   int heads, head_size, hidden_size;
@@ -1088,7 +1107,17 @@ extern "C" int aps_hybrid_decode_attention(void* out, const void* query, const v
   const char* pk = getenv("APS_PACK_TILES");
   const bool pack_tiles = tensor_path && !(pk != nullptr && pk[0] == '0');
   if ((st = launch_plan(ws, seq_lens, cache_type, batch, max_blocks_per_seq, block_size, pack_tiles, cs)) != APS_OK) return st;
-  if (key_cache != nullptr && value_cache != nullptr) {
+  // K/V requests: on the call's stream before the re-projection kernel.  APS_OVERLAP=1 puts
+  // the K/V kernel on a side stream beside the re-projection kernel instead (the combine then
+  // waits for both); measured slower (the 4 K/V warps per SM that fit beside the 320-thread
+  // re-projection CTA stream at a small fraction of the HBM rate), so it is off by default
+  const char* ov = getenv("APS_OVERLAP");
+  const bool have_kv = key_cache != nullptr && value_cache != nullptr;
+  SideStream* side = nullptr;
+  if (have_kv && tensor_path && ov != nullptr && ov[0] == '1') {
+    if ((st = side_stream(&side)) != APS_OK) return st;
+  }
+  if (have_kv && side == nullptr) {
     if ((st = launch_kv_attention(ws, query, key_cache, value_cache, block_tables, seq_lens, s, cs)) != APS_OK) return st;
   }
   if (!tensor_path) {
@@ -1108,9 +1137,18 @@ extern "C" int aps_hybrid_decode_attention(void* out, const void* query, const v
   p.x_base = hidden_cache; p.x_row_bytes = hidden_row_stride * 2; p.x_rows = num_hidden_rows; p.hidden_mult64 = hidden_size % 64 == 0;
   p.status = ws.plan + kPlanStatus;
   p.stats = getenv("APS_STATS") != nullptr ? reinterpret_cast<unsigned long long*>(ws.plan + kPlanStatsWord) : nullptr;
+  if (side != nullptr) APS_CUDA(cudaEventRecord(side->forked, cs));
   st = dtype == APS_BF16 ? launch_hidden<__nv_bfloat16, kModeAttend>(mx, mk, mv, p, cs)
                          : launch_hidden<__half, kModeAttend>(mx, mk, mv, p, cs);
   if (st != APS_OK) return st;
+  if (side != nullptr) {
+    APS_CUDA(cudaStreamWaitEvent(side->stream, side->forked, 0));
+    AttnShape s2 = s;
+    s2.side_by_side = true;
+    if ((st = launch_kv_attention(ws, query, key_cache, value_cache, block_tables, seq_lens, s2, side->stream)) != APS_OK) return st;
+    APS_CUDA(cudaEventRecord(side->joined, side->stream));
+    APS_CUDA(cudaStreamWaitEvent(cs, side->joined, 0));
+  }
   return launch_combine(ws, out, seq_lens, s, cs);
 }
 

@@ -155,7 +155,7 @@ kv_attention_kernel(int* __restrict__ plan, const int* __restrict__ part_offset,
   const int64_t row_stride = (int64_t)heads * D;
 
   while (true) {
-    if (threadIdx.x == 0) s_base = atomicAdd(&plan[kPlanKvCounter], kKvWarps);
+    if (threadIdx.x == 0) s_base = atomicAdd(&plan[kPlanKvCounter], (int)(blockDim.x >> 5));
     __syncthreads();
     const int base = s_base;
     __syncthreads();
@@ -288,10 +288,13 @@ template <typename T, int D>
 int launch_kv_typed(const WorkspacePtrs& ws, const void* query, const void* key_cache,
                     const void* value_cache, const int32_t* block_tables, const int32_t* seq_lens,
                     const AttnShape& s, cudaStream_t stream) {
-  const int grid = sm_count() * 2;
+  // alone on the GPU: 2 CTAs of 8 warps per SM.  Beside the re-projection kernel (which keeps
+  // one 320-thread CTA and most of the registers on every SM): 1 CTA of 4 warps per SM.
+  const int grid = s.side_by_side ? sm_count() : sm_count() * 2;
+  const int threads = s.side_by_side ? 4 * 32 : kKvWarps * 32;
   const float scale_log2 = s.scale * 1.4426950408889634f;
   ScopedProfile prof(0, stream);
-  kv_attention_kernel<T, D><<<grid, kKvWarps * 32, 0, stream>>>(
+  kv_attention_kernel<T, D><<<grid, threads, 0, stream>>>(
       ws.plan, ws.part_offset, ws.kv_chunks, ws.part_ml, ws.part_acc, (const T*)query,
       (const T*)key_cache, (const T*)value_cache, block_tables, seq_lens, s.max_blocks_per_seq,
       s.heads, s.block_size, s.query_stride, s.block_stride, scale_log2);

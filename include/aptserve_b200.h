@@ -19,8 +19,8 @@
  *  - every call enqueues on `stream` (a cudaStream_t passed as void*) of the
  *    CURRENT device and returns without synchronising;
  *  - nothing is allocated or freed for the caller and no pointer is retained
- *    after return, except the per-device objects created by aps_* on first use
- *    (an auxiliary stream, two events) which live until process exit;
+ *    after return (with APS_OVERLAP=1 in the environment the hybrid call creates a
+ *    per-device side stream and two events on first use, kept until process exit);
  *  - the return value is an aps_status; no C++ exception crosses the boundary;
  *    aps_last_error() gives a human-readable message for the calling thread.
  */
