@@ -10,33 +10,41 @@
 // Here the hidden rows go HBM -> shared memory (TMA) -> tensor cores -> TMEM ->
 // registers -> softmax partial; K and V never exist in global memory.
 //
-// One M tile = 128 cached tokens of one hidden request; for head h the tile's
-// 128 x 256 block [K_h | V_h] = X_tile * [W_k,h ; W_v,h]^T is accumulated in fp32 in
-// tensor memory.  Warp roles in every CTA:
-//   warp 0    TMA producer: per 64-element slab of the hidden dimension, one
-//             16-row box per cache block of the tile (hidden blocks are paged)
-//             plus the W rows of head h, 128-byte swizzle, multi-stage ring;
+// One M tile = 128 cached token rows, taken 16 at a time (one paged cache block each)
+// from the hidden requests in batch order, so a tile can hold rows of several requests and
+// only the last tile is partly empty.  For head h the tile's 128 x 256 block
+// [K_h | V_h] = X_tile * [W_k,h ; W_v,h]^T is accumulated in fp32 in tensor memory.
+// Warp roles in every CTA (320 threads):
+//   warp 0, warps 6-9  TMA producers: per 64-element slab of the hidden dimension warp 0
+//             posts the stage's byte count and issues the W boxes of head h, warps 6-9
+//             issue two 16-row boxes (two cache blocks of the tile) each; 128-byte swizzle,
+//             multi-stage ring.  One thread cannot issue ten tensor copies in the 512
+//             cycles the tensor cores need for a slab, hence the split;
 //   warp 1    tcgen05.mma issuer (K = 16 per instruction, 4 per slab); the
 //             accumulator is double-buffered in the 512 TMEM columns, so the main
 //             loop of item i+1 overlaps the epilogue of item i;
 //   warps 2-5 epilogue: one thread per token row reads its K row from TMEM, adds
-//             b_k, dots with q (pre-scaled by scale*log2 e), block-wide max, then
-//             reads its V row, weighs it and column-sums over the 128 rows with a
-//             shuffle butterfly; the (max, sum, acc[128]) partial goes to scratch.
+//             b_k, dots with its request's q (pre-scaled by scale*log2 e); maxima, sums
+//             and the weighted V column sums are formed per 16-row block with half-warp
+//             shuffles and merged per request segment; one (max, sum, acc[128]) partial
+//             per (segment, head) goes to scratch.
 //
 // Two variants of the main loop:
-//   single   one CTA per SM works alone: M128 N256 instructions, both W boxes
-//            loaded by the CTA, 4 stages of 48 KB.  Shared memory then carries
-//            96 B/clk of operand reads plus 96 B/clk of TMA writes.
-//   pair     two CTAs of a cluster (cta_group::2) work on two M tiles of the same
-//            head with one M256 N256 instruction stream issued by the even CTA:
+//   pair     (default) two CTAs of a cluster (cta_group::2) work on two M tiles of the
+//            same head with one M256 N256 instruction stream issued by the even CTA:
 //            each CTA loads its own X tile and HALF of the W rows (even CTA: W_k,h,
 //            odd CTA: W_v,h), the tensor cores read both halves, 6 stages of 32 KB.
-//            Shared-memory traffic per SM drops to 64 + 64 B/clk.  Loads carry no
-//            multicast: each CTA fetches what it needs itself; the two CTAs
-//            only exchange mbarrier arrivals.
-// CTAs are persistent and walk the items in a rasterised order (a group of M tiles
-// x all heads) so that hidden tiles and W slabs are shared through L2.
+//            Loads carry no multicast: each CTA fetches what it needs itself; the two
+//            CTAs only exchange mbarrier arrivals.
+//   single   one CTA per SM works alone: M128 N256 instructions, both W boxes
+//            loaded by the CTA, 4 stages of 48 KB.
+// CTAs are persistent and walk the items in groups (a few M tiles x a few heads) so
+// that hidden tiles and W slabs are shared through L2.
+//
+// Environment knobs (read at call time): APS_HIDDEN_VARIANT=single|pair,
+// APS_RASTER=units,heads, APS_PACK_TILES=0, APS_SPLIT_ISSUE=0, APS_A_MODE=loaders (hidden
+// rows by cp.async loader warps, single variant), APS_STATS=1 (cycle counters in the
+// scratch header), APS_FORCE_SIMT=1, APS_OVERLAP=1, APS_DENSE_A=0.
 //
 // Every mbarrier wait is bounded by a clock budget; a wait that runs out records
 // a code in the plan's status word, tells the other warps through shared memory,
@@ -160,24 +168,9 @@ __device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t rank) {
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar,
-                                            int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
-      : "memory");
-}
-// Load into this CTA's shared memory, completion bytes counted on a barrier that
-// may live in the peer CTA of the pair (given as a shared::cluster address).
-__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map,
-                                                 uint32_t bar_cluster_addr, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y)
-      : "memory");
-}
-// Same two copies, with the shared-memory destination and the barrier already given as
-// 32-bit shared addresses.
+// Tensor copies (TMA): a box of the tensor map lands in this CTA's shared memory, the bytes
+// are counted on an mbarrier.  The pair form may name a barrier of the peer CTA (given as a
+// shared::cluster address).  Destination and barrier are 32-bit shared addresses.
 __device__ __forceinline__ void tma_load_2d_a(uint32_t smem_dst, const CUtensorMap* map, uint32_t bar,
                                               int x, int y) {
   asm volatile(
@@ -288,9 +281,7 @@ struct HiddenParams {
   int raster_heads;           // heads per group of the work order
   int dense_a;                // X rows of a tile are contiguous: map_x has a 128-row box
   int a_mode;                 // 0: hidden rows by TMA boxes, 1: by the loader warps (cp.async)
-  int b_skip;                 // timing experiment only: do not load W (results are garbage)
   int split_issue;            // the boxes of a stage are issued by four producer threads
-  int debug;                  // timing experiments only: bit 0 skip epilogue math, bit 1 producer ignores empty
   int hidden_mult64;          // hidden size is a multiple of 64 elements
   const void* x_base;         // first row of the hidden cache / X matrix (a_mode 1)
   int64_t x_row_bytes;        // its row stride in bytes
@@ -543,7 +534,7 @@ __device__ __forceinline__ void tma_producer(const HiddenParams& p, SmemAux* aux
   constexpr int kStageBytes = kABytes + V::kBBytes;
   volatile int* abort_flag = &aux->abort_flag;
   const bool leader = rank == 0;
-  const bool loaders = !PAIR && p.a_mode >= 1;   // hidden rows come from the loader warps
+  const bool loaders = !PAIR && p.a_mode == 1;   // hidden rows come from the loader warps
   const bool split = p.split_issue != 0 && !loaders;   // else producer 0 issues everything
   if (!split && prod != 0) return;
   uint32_t stage = 0, phase = 0;
@@ -553,7 +544,7 @@ __device__ __forceinline__ void tma_producer(const HiddenParams& p, SmemAux* aux
   for (int i = first; i < n_items && ok; i += stride) {
     const Item it = item_of(i, n_units, p.heads, p.raster_units, p.raster_heads);
     const int tile = PAIR ? it.unit * 2 + (int)rank : it.unit;
-    const int n_sub = (loaders || p.a_mode == 3) ? 0 : tile_n_sub<MODE>(p, tile, n_tiles);
+    const int n_sub = loaders ? 0 : tile_n_sub<MODE>(p, tile, n_tiles);
     int sub_row[kSubsPerTile];
     tile_sub_rows<MODE>(p, n_sub > 0 ? tile : 0, n_sub, sub_row);
     // a dense X tile is one 128-row box (rows past the end are zero-filled and still
@@ -561,15 +552,14 @@ __device__ __forceinline__ void tma_producer(const HiddenParams& p, SmemAux* aux
     const bool dense = p.dense_a != 0;
     uint32_t tx_bytes = (uint32_t)((dense ? (n_sub > 0 ? kABytes : 0) : n_sub * kSubBytes) + V::kBBytes);
     if (PAIR && leader) {
-      const int peer_sub = p.a_mode == 3 ? 0 : tile_n_sub<MODE>(p, tile + 1, n_tiles);
+      const int peer_sub = tile_n_sub<MODE>(p, tile + 1, n_tiles);
       tx_bytes += (uint32_t)((dense ? (peer_sub > 0 ? kABytes : 0) : peer_sub * kSubBytes) + V::kBBytes);
     }
-    if (p.b_skip) tx_bytes -= (PAIR && leader ? 2 : 1) * V::kBBytes;
     // the boxes this producer issues.  With the split, a producer owns two fixed block
     // slots, so its loop holds at most four copy instructions (a copy instruction that is
     // predicated off still costs the thread some twenty cycles).
-    const bool do_w0 = !p.b_skip && prod == 0;                         // W_k (single) / this CTA's half (pair)
-    const bool do_w1 = !p.b_skip && !PAIR && prod == 0;                // W_v (single)
+    const bool do_w0 = prod == 0;                         // W_k (single) / this CTA's half (pair)
+    const bool do_w1 = !PAIR && prod == 0;                // W_v (single)
     const bool do_dense = dense && prod == 0 && n_sub > 0;
     const bool post = prod == 0 && (!PAIR || leader);                  // posts the stage's byte count
     const CUtensorMap* w0_map = PAIR ? (leader ? &map_wk : &map_wv) : &map_wk;
@@ -612,11 +602,6 @@ __device__ __forceinline__ void tma_producer(const HiddenParams& p, SmemAux* aux
         const long long t0 = (p.stats && prod == 0) ? clock64() : 0;
         if (!mbar_wait(&aux->empty[stage], phase ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
         const long long t1 = (p.stats && prod == 0) ? clock64() : 0;
-        if (p.debug & 32) {   // experiment: no copy instructions in the loop at all
-          if (post) mbar_expect_tx(&aux->full[stage], 0);
-          if (++stage == kStages) { stage = 0; phase ^= 1; }
-          continue;
-        }
         const uint32_t a_dst = smem_base + stage * kStageBytes;
         const uint32_t b_dst = a_dst + kABytes;
         const uint32_t bar_local = full_base + stage * 8;
@@ -679,7 +664,7 @@ hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
   if (threadIdx.x == 0) {
     // full[s]: one arrival from the TMA producer (with the byte count of its boxes), plus one
     // per loader thread when the hidden rows are brought in by the loader warps
-    const uint32_t full_count = 1u + ((!PAIR && p.a_mode >= 1) ? (uint32_t)kLoaderThreads : 0u);
+    const uint32_t full_count = 1u + ((!PAIR && p.a_mode == 1) ? (uint32_t)kLoaderThreads : 0u);
     for (int s = 0; s < kStages; ++s) { mbar_init(&aux->full[s], full_count); mbar_init(&aux->empty[s], 1); }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&aux->acc_full[b], 1);
@@ -734,14 +719,10 @@ hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         const uint32_t d_tmem = tmem_base + buf * kBN;
         for (int ks = 0; ks < p.k_slabs; ++ks) {
           t0 = st ? clock64() : 0;
-          if (p.debug & 16) {   // experiment: non-suspending poll
-            uint32_t okk = 0;
-            while (!okk) asm volatile("{.reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0,1,0,p;}" : "=r"(okk) : "r"(smem_u32(&aux->full[stage])), "r"(phase) : "memory");
-          } else
-          if (!(p.debug & 4) && !mbar_wait(&aux->full[stage], phase, abort_flag, p.status, 3)) { ok = false; break; }
+          if (!mbar_wait(&aux->full[stage], phase, abort_flag, p.status, 3)) { ok = false; break; }
           if (st) { const long long dt = clock64() - t0; w_full += dt; if (ks == 0) w_first += dt; }
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(smem + (size_t)((p.debug & 8) ? 0 : stage) * kStageBytes);
+          const uint32_t a_addr = smem_u32(smem + (size_t)stage * kStageBytes);
           const uint64_t a_desc = smem_desc_sw128(a_addr);
           const uint64_t b_desc = smem_desc_sw128(a_addr + kABytes);
 #pragma unroll
@@ -791,7 +772,7 @@ hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     // cache block of the tile into the 128-byte-swizzled stage (chunk index XOR row % 8),
     // and the stage's barrier counts one arrival per thread, delivered by the copy unit when
     // that thread's copies have landed.  The W boxes stay on TMA.
-    if (!(!PAIR && p.a_mode >= 1)) {
+    if (!(!PAIR && p.a_mode == 1)) {
       // TMA mode: warps 6..9 are producers 1..4
       const int prod = warp - 5;   // warps 6..9 -> producers 1..4
       if (prod > 0 && lane == 0)
@@ -829,7 +810,7 @@ hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
           const uint32_t dst = smem_u32(smem + (size_t)stage * kStageBytes) + swz;
 #pragma unroll
           for (int c = 0; c < kSubsPerTile; ++c)
-            if (c < n_sub && p.a_mode == 1)
+            if (c < n_sub)
               asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + c * kSubBytes),
                            "l"(src[c] + (int64_t)ks * kBKBytes), "r"(((in_range >> c) & 1u) * 16u) : "memory");
           // arrives on the stage's barrier when this thread's copies above have landed
@@ -870,8 +851,7 @@ hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
           else mbar_arrive(acc_empty);
         }
       };
-      if (p.debug & 1) { release(); epi_barrier(); }
-      else epilogue_compute<T, MODE>(aux, p, t_row, tile, tile_ok, it.head, quarter, lane, et, release);
+      epilogue_compute<T, MODE>(aux, p, t_row, tile, tile_ok, it.head, quarter, lane, et, release);
       (void)t0; (void)t1;
     }
   }
@@ -995,10 +975,6 @@ int launch_hidden(const CUtensorMap& mx, const CUtensorMap& mk, const CUtensorMa
   const char* am = getenv("APS_A_MODE");
   const bool want_loaders = am != nullptr && strcmp(am, "loaders") == 0;
   p.a_mode = (want_loaders && !p.dense_a && p.x_base != nullptr && p.hidden_mult64) ? 1 : 0;
-  if (am != nullptr && strcmp(am, "skip") == 0) p.a_mode = 2;      // timing experiment only
-  if (am != nullptr && strcmp(am, "skiptma") == 0) p.a_mode = 3;   // timing experiment only
-  p.b_skip = getenv("APS_B_SKIP") != nullptr ? 1 : 0;
-  p.debug = getenv("APS_DEBUG") != nullptr ? atoi(getenv("APS_DEBUG")) : 0;
   const char* si = getenv("APS_SPLIT_ISSUE");
   p.split_issue = (si != nullptr && si[0] == '0') ? 0 : 1;
   return use_pair_variant() ? launch_hidden_variant<T, MODE, true>(mx, mk, mv, p, stream)

@@ -400,7 +400,9 @@ def run_ours(args):
                            "new-token cache writes + hybrid decode attention" +
                            (" + o_proj + all-reduce" if tp > 1 else ""),
                    "parallelism": f"tp{tp}" if tp > 1 else "single GPU",
-                   "l2": f"inputs larger than L2: {(work['kv_attention_bytes'] + work['hidden_bytes']) / 1e9:.2f} GB streamed per step",
+                   "l2": (f"inputs larger than L2: {(work['kv_attention_bytes'] + work['hidden_bytes']) / 1e9:.2f} GB streamed per step"
+                          if work['kv_attention_bytes'] + work['hidden_bytes'] > 256e6 else
+                          f"working set {(work['kv_attention_bytes'] + work['hidden_bytes']) / 1e6:.1f} MB fits in L2: the number is L2-warm"),
                    "seed": seed},
         "clocks": clocks,
         "e2e": {"value": round(B / e2e_s, 2), "unit": UNIT, "h2d_bytes_per_step": h2d,
