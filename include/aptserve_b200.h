@@ -245,6 +245,41 @@ int aps_kv_reprojection(void* kv, const void* x, const int32_t* block_ids, int64
  */
 int aps_attention_status(const void* workspace, int* host_status, void* stream);
 
+/* ------------------------------------------------------------------------ */
+/* Index tensors                                                             */
+/* ------------------------------------------------------------------------ */
+
+/*
+ * Replaces the decode branch of ModelRunner._prepare_model_input
+ * (additional_designs/worker/aptserve_model_runner.py:515-564 per-request loop,
+ * :613-648 mask-to-index conversion): expands the block tables on the device into
+ * the eight int64 index tensors of a decode batch, instead of building them with a
+ * Python loop over every cached position of every hidden-cached request and copying
+ * them to the device each step.
+ *   block_tables         int32 [B, max_blocks]  private tables (hidden requests: V-plane ids for odd blocks)
+ *   block_tables_shared  int32 [B, max_blocks]  shared tables of hidden requests (rows of K/V requests unused)
+ *   seq_lens int32 [B] (>= 1, includes the token being decoded), cache_type int32 [B]
+ * Outputs (sizes as in the reference: N_tot = sum over hidden requests of S_r + number of
+ * K/V requests, N_h = sum over hidden requests of S_r, n_kv, n_h = request counts):
+ *   slot_mapping [N_tot], slot_mapping_shared [N_h], hidden_cache_use_tot [N_h],
+ *   kv_cache_use_tot [n_kv], hidden_holder_upd [B], hidden_holder_pull [N_tot - B],
+ *   hidden_cache_store_tot [n_h], hidden_cache_use_input [n_h].
+ * num_tot_tokens / num_hidden_tokens are the capacities of the N_tot / N_h tensors (the
+ * host knows them from the sequence lengths); nothing is written past them.  counts
+ * (device int64[4], may be NULL) receives N_tot, N_h, n_kv, n_h as computed on the device.
+ * scratch: aps_decode_metadata_scratch_bytes(B) bytes of device memory.
+ */
+size_t aps_decode_metadata_scratch_bytes(int batch);
+int aps_expand_decode_metadata(const int32_t* block_tables, const int32_t* block_tables_shared,
+                               const int32_t* seq_lens, const int32_t* cache_type, int batch,
+                               int max_blocks_per_seq, int block_size, int64_t* slot_mapping,
+                               int64_t* slot_mapping_shared, int64_t* hidden_cache_use_tot,
+                               int64_t* kv_cache_use_tot, int64_t* hidden_holder_upd,
+                               int64_t* hidden_holder_pull, int64_t* hidden_cache_store_tot,
+                               int64_t* hidden_cache_use_input, int64_t num_tot_tokens,
+                               int64_t num_hidden_tokens, int64_t* counts, void* scratch,
+                               size_t scratch_bytes, void* stream);
+
 /*
  * Timing hook for benchmarks (no counterpart in the reference, whose kernels are
  * timed with commented-out torch.cuda.synchronize() calls, fa.py:374-387):
