@@ -98,6 +98,43 @@ cache_to_hidden_kernel(char* __restrict__ hidden, const char* __restrict__ paged
   }
 }
 
+// Prefill cache write in one pass over the packed prompt tokens, as a flat list of row
+// copies: jobs [0, 2 n_kv) copy the K row (even job) or the V row (odd job) of token
+// kv_rows[job / 2] into the K / V plane; jobs [2 n_kv, 2 n_kv + n_hidden) copy the
+// layer-input row of token hidden_rows[j] into the flat hidden rows.  Every token's slot is
+// slot_mapping[token].
+template <typename V>
+__global__ void __launch_bounds__(kCopyThreads)
+prefill_write_kernel(const char* __restrict__ key, const char* __restrict__ value,
+                     const char* __restrict__ hidden, char* __restrict__ key_cache,
+                     char* __restrict__ value_cache, char* __restrict__ hidden_cache,
+                     const int64_t* __restrict__ slot_mapping, const int64_t* __restrict__ kv_rows,
+                     int64_t n_kv, const int64_t* __restrict__ hidden_rows, int64_t n_hidden,
+                     int64_t key_stride_b, int64_t value_stride_b, int64_t hidden_stride_b,
+                     int64_t block_stride_b, int64_t slot_stride_b, int64_t kv_row_bytes,
+                     int64_t hidden_row_bytes, int block_size) {
+  for (int64_t job = blockIdx.x; job < 2 * n_kv + n_hidden; job += gridDim.x) {
+    if (job < 2 * n_kv) {
+      const int64_t tok = kv_rows[job >> 1];
+      const int64_t slot = slot_mapping[tok];
+      if (slot < 0) continue;
+      const int64_t off = (slot / block_size) * block_stride_b + (slot % block_size) * kv_row_bytes;
+      const int n_vec = static_cast<int>(kv_row_bytes / sizeof(V));
+      if ((job & 1) == 0)
+        copy_row(reinterpret_cast<V*>(key_cache + off), reinterpret_cast<const V*>(key + tok * key_stride_b), n_vec);
+      else
+        copy_row(reinterpret_cast<V*>(value_cache + off), reinterpret_cast<const V*>(value + tok * value_stride_b), n_vec);
+    } else {
+      const int64_t tok = hidden_rows[job - 2 * n_kv];
+      const int64_t slot = slot_mapping[tok];
+      if (slot < 0) continue;
+      copy_row(reinterpret_cast<V*>(hidden_cache + slot * slot_stride_b),
+               reinterpret_cast<const V*>(hidden + tok * hidden_stride_b),
+               static_cast<int>(hidden_row_bytes / sizeof(V)));
+    }
+  }
+}
+
 // Jobs [0, n_kv): a K/V request's new token goes to the private cache and, at
 // the same slot, to the shared cache (one read, two writes).  Jobs
 // [n_kv, n_kv + n_hidden): a hidden request's re-projected token goes to the
@@ -324,6 +361,53 @@ extern "C" int aps_mixed_kv_to_cache(const void* key, const void* value, void* k
       hidden_cache_use_tot, n_kv, n_hidden, key_stride * es, value_stride * es, block_stride * es,
       shared_block_stride * es, row * es, block_size));
   return launch_status("mixed_kv_to_cache_kernel");
+}
+
+extern "C" int aps_prefill_cache_write(const void* key, const void* value, const void* hidden,
+                                       void* key_cache, void* value_cache, void* hidden_cache,
+                                       const int64_t* slot_mapping, const int64_t* kv_rows,
+                                       int64_t n_kv, const int64_t* hidden_rows, int64_t n_hidden,
+                                       int num_heads, int head_size, int hidden_size, int block_size,
+                                       int64_t key_stride, int64_t value_stride, int64_t hidden_stride,
+                                       int64_t block_stride, int64_t slot_stride, int dtype,
+                                       void* stream) {
+  const int es = dtype_size(dtype);
+  APS_REQUIRE(es != 0, APS_ERR_DTYPE, "prefill_cache_write: unsupported dtype %d", dtype);
+  APS_REQUIRE(n_kv >= 0 && n_hidden >= 0 && num_heads > 0 && head_size > 0 && hidden_size > 0 &&
+                  block_size > 0,
+              APS_ERR_SHAPE, "prefill_cache_write: bad sizes");
+  if (n_kv + n_hidden == 0) return APS_OK;
+  APS_REQUIRE(slot_mapping != nullptr, APS_ERR_NULL_POINTER, "prefill_cache_write: null pointer");
+  APS_REQUIRE(n_kv == 0 || (key && value && key_cache && value_cache && kv_rows), APS_ERR_NULL_POINTER,
+              "prefill_cache_write: null pointer (K/V arguments)");
+  APS_REQUIRE(n_hidden == 0 || (hidden && hidden_cache && hidden_rows), APS_ERR_NULL_POINTER,
+              "prefill_cache_write: null pointer (hidden arguments)");
+  const int64_t row = (int64_t)num_heads * head_size;
+  APS_REQUIRE(n_kv == 0 || (key_stride >= row && value_stride >= row && block_stride >= row * block_size),
+              APS_ERR_SHAPE, "prefill_cache_write: K/V strides smaller than a row / block");
+  APS_REQUIRE(n_hidden == 0 || (hidden_stride >= hidden_size && slot_stride > 0), APS_ERR_SHAPE,
+              "prefill_cache_write: bad hidden strides");
+  int vb = 16;
+  if (n_kv > 0)
+    vb = common_vector_bytes({(uint64_t)(uintptr_t)key, (uint64_t)(uintptr_t)value,
+                              (uint64_t)(uintptr_t)key_cache, (uint64_t)(uintptr_t)value_cache,
+                              (uint64_t)row * es, (uint64_t)key_stride * es, (uint64_t)value_stride * es,
+                              (uint64_t)block_stride * es});
+  if (n_hidden > 0) {
+    const int vh = common_vector_bytes({(uint64_t)(uintptr_t)hidden, (uint64_t)(uintptr_t)hidden_cache,
+                                        (uint64_t)hidden_size * es, (uint64_t)hidden_stride * es,
+                                        (uint64_t)slot_stride * es});
+    vb = vh < vb ? vh : vb;
+  }
+  APS_REQUIRE(vb >= es, APS_ERR_MISALIGNED, "prefill_cache_write: pointer not aligned to its element size");
+  const unsigned grid = grid_for(2 * n_kv + n_hidden);
+  const int64_t widest = row > hidden_size ? row : hidden_size;
+  APS_DISPATCH_VEC(vb, prefill_write_kernel<V><<<grid, threads_for(widest * es / vb), 0, (cudaStream_t)stream>>>(
+      (const char*)key, (const char*)value, (const char*)hidden, (char*)key_cache, (char*)value_cache,
+      (char*)hidden_cache, slot_mapping, kv_rows, n_kv, hidden_rows, n_hidden, key_stride * es,
+      value_stride * es, hidden_stride * es, block_stride * es, slot_stride * es, row * es,
+      (int64_t)hidden_size * es, block_size));
+  return launch_status("prefill_write_kernel");
 }
 
 extern "C" int aps_copy_blocks(void* const* key_cache_ptrs, void* const* value_cache_ptrs,

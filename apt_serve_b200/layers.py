@@ -89,8 +89,9 @@ class OPTAttention(torch.nn.Module):
     projection, ``mixed_kv_to_cache`` scatter, paged attention over the shared
     cache -- into: Q projection, the new token's K/V projection and cache write
     for K/V requests, the new token's hidden row write for hidden requests, one
-    hybrid decode attention call.  ``fused=False`` runs the reference's op
-    sequence literally on this package's kernels.
+    hybrid decode attention call; a prefill batch with hidden-designated prompts
+    writes both kinds of cache rows with one launch.  ``fused=False`` runs the
+    reference's op sequence literally on this package's kernels.
 
     Under tensor parallelism ``hidden_cache`` must be given (a
     ``[2, NB, BS, 1, E]`` tensor replicated per rank); with one rank it defaults
@@ -117,6 +118,20 @@ class OPTAttention(torch.nn.Module):
                 hidden_cache: Optional[torch.Tensor] = None) -> torch.Tensor:
         m = attn_metadata
         hcache = kv_cache if hidden_cache is None else hidden_cache
+        if (self.fused and m.num_hidden_cache_tokens != 0 and m.num_decode_tokens == 0
+                and kv_cache is not None):
+            # prefill with hidden-designated prompts: one launch writes the K/V rows of the
+            # K/V-designated tokens and the layer-input rows of the hidden-designated ones;
+            # the attention below then runs without a cache (nothing left to write)
+            qkv, _ = self.qkv_proj(hidden_states)
+            q, k, v = qkv.chunk(chunks=3, dim=-1)
+            ops.prefill_cache_write(k.view(-1, self.num_heads, self.head_dim),
+                                    v.view(-1, self.num_heads, self.head_dim), hidden_states,
+                                    kv_cache, hcache, m.slot_mapping, m.kv_cache_use_tot,
+                                    m.hidden_cache_use_input)
+            attn_output = self.attn(q, k, v, None, shared_cache, m)
+            output, _ = self.out_proj(attn_output)
+            return output
         if m.num_hidden_cache_tokens != 0:
             mixed_cache_ops.hidden_to_cache(hidden_states, hcache, m.slot_mapping,
                                             m.hidden_cache_use_input, m.hidden_cache_store_tot)

@@ -35,6 +35,35 @@ def reshape_and_cache_flash(key: torch.Tensor, value: torch.Tensor, key_cache: t
             N.dtype_enum(key), N.current_stream(dev)))
 
 
+def prefill_cache_write(key: torch.Tensor, value: torch.Tensor, hidden_states: torch.Tensor,
+                        kv_cache: torch.Tensor, hidden_cache: torch.Tensor,
+                        slot_mapping: torch.Tensor, kv_cache_use_tot: torch.Tensor,
+                        hidden_cache_use_input: torch.Tensor) -> None:
+    """One launch for a prefill batch's cache writes: K/V rows of the K/V-designated
+    prompt tokens (``kv_cache_use_tot``) into ``kv_cache``, layer-input rows of the
+    hidden-designated ones (``hidden_cache_use_input``) into the flat rows of
+    ``hidden_cache``; every token's slot is ``slot_mapping[token]``.  Stands in for
+    ``hidden_to_cache`` + ``reshape_and_cache_flash(key[kv_cache_use_tot], ...)``
+    (aptserve_opt.py:108-109, aptserve_flash_attn.py:347-355) without the gathered copies.
+    ``key`` / ``value``: ``[T, H, D]``; ``hidden_states``: ``[T, E]``."""
+    dev = N.require_cuda(key, value, hidden_states, kv_cache, hidden_cache, slot_mapping,
+                         kv_cache_use_tot, hidden_cache_use_input)
+    for t, name in ((slot_mapping, "slot_mapping"), (kv_cache_use_tot, "kv_cache_use_tot"),
+                    (hidden_cache_use_input, "hidden_cache_use_input")):
+        if t.dtype != torch.int64:
+            raise RuntimeError(f"{name} must be int64")
+    if not (key.dtype == value.dtype == hidden_states.dtype == kv_cache.dtype == hidden_cache.dtype):
+        raise RuntimeError("prefill_cache_write: dtypes differ")
+    with torch.cuda.device(dev):
+        N.check(N.lib().aps_prefill_cache_write(
+            N.ptr(key), N.ptr(value), N.ptr(hidden_states), N.ptr(kv_cache[0]), N.ptr(kv_cache[1]),
+            N.ptr(hidden_cache), N.ptr(slot_mapping.contiguous()), N.ptr(kv_cache_use_tot.contiguous()),
+            kv_cache_use_tot.numel(), N.ptr(hidden_cache_use_input.contiguous()),
+            hidden_cache_use_input.numel(), key.size(1), key.size(2), hidden_states.size(1),
+            kv_cache.size(2), key.stride(0), value.stride(0), hidden_states.stride(0),
+            kv_cache.stride(1), hidden_cache.stride(2), N.dtype_enum(key), N.current_stream(dev)))
+
+
 def copy_blocks(key_caches: List[torch.Tensor], value_caches: List[torch.Tensor],
                 block_mapping: torch.Tensor) -> None:
     """Copy-on-write block copies for every layer; ``block_mapping`` is an int64

@@ -165,6 +165,7 @@ class LayerStep:
         self.kv_new_slots = torch.where(m.cache_type != 0, torch.full_like(new_slot, -1), new_slot)
         self.out = torch.empty_like(w.query)
         self.prefill_events = None   # (start, stop) recorded around prefill_writes when set
+        self.fused_prefill_write = os.environ.get("APS_BENCH_FUSED_PREFILL_WRITE") is not None
         self.workspace = A.attention_workspace(w.query.device, w.query.shape[0],
                                                m.private_block_tables.shape[1], w.shape.block_size, h, d)
 
@@ -198,10 +199,14 @@ class LayerStep:
             slots = torch.full_like(pm.slot_mapping, -1)
             slots[pm.kv_cache_use_tot] = pm.slot_mapping[pm.kv_cache_use_tot]
             self._prefill_kv_slots = slots
-        ops.reshape_and_cache_flash(pf.key, pf.value, w.kv_cache[0], w.kv_cache[1],
-                                    self._prefill_kv_slots, "auto")
-        mixed_cache_ops.hidden_to_cache(pf.hidden_states, w.hidden_cache, pm.slot_mapping,
-                                        pm.hidden_cache_use_input, pm.hidden_cache_store_tot)
+        if self.fused_prefill_write:
+            ops.prefill_cache_write(pf.key, pf.value, pf.hidden_states, w.kv_cache, w.hidden_cache,
+                                    pm.slot_mapping, pm.kv_cache_use_tot, pm.hidden_cache_use_input)
+        else:
+            ops.reshape_and_cache_flash(pf.key, pf.value, w.kv_cache[0], w.kv_cache[1],
+                                        self._prefill_kv_slots, "auto")
+            mixed_cache_ops.hidden_to_cache(pf.hidden_states, w.hidden_cache, pm.slot_mapping,
+                                            pm.hidden_cache_use_input, pm.hidden_cache_store_tot)
         if w.copy_pairs is not None:
             FlashAttentionBackend.copy_blocks([w.kv_cache], w.copy_pairs)
 

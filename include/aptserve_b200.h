@@ -120,6 +120,24 @@ int aps_mixed_kv_to_cache(const void* key, const void* value, void* k_cache,
                           void* stream);
 
 /*
+ * Prefill cache write in one launch: replaces the pair of calls a prefill batch with
+ * hidden-designated prompts makes -- mixed_cache_ops.hidden_to_cache for the hidden-designated
+ * token rows (opt.py:108-109) and reshape_and_cache_flash on the index-selected
+ * key[kv_cache_use_tot] / value[kv_cache_use_tot] (fa.py:347-355):
+ *   i in [0, n_kv):     t = kv_rows[i];     key/value[t] -> K / V plane at slot_mapping[t]
+ *   j in [0, n_hidden): t = hidden_rows[j]; hidden[t, :]  -> flat hidden row slot_mapping[t]
+ * kv_rows / hidden_rows are the metadata's kv_cache_use_tot / hidden_cache_use_input.
+ * No gathered copy of key / value is made.
+ */
+int aps_prefill_cache_write(const void* key, const void* value, const void* hidden,
+                            void* key_cache, void* value_cache, void* hidden_cache,
+                            const int64_t* slot_mapping, const int64_t* kv_rows, int64_t n_kv,
+                            const int64_t* hidden_rows, int64_t n_hidden, int num_heads,
+                            int head_size, int hidden_size, int block_size, int64_t key_stride,
+                            int64_t value_stride, int64_t hidden_stride, int64_t block_stride,
+                            int64_t slot_stride, int dtype, void* stream);
+
+/*
  * Replaces vllm._custom_ops.copy_blocks as called at fa.py:58-65:
  * for every layer l and every row (src, dst) of block_mapping [num_pairs, 2]:
  *   key_caches[l][dst] = key_caches[l][src]; value_caches[l][dst] = value_caches[l][src].

@@ -290,3 +290,32 @@ def test_flash_attention_impl_kv_only_decode_and_prefill_write():
     out = impl.forward(w.query, w.new_key, w.new_value, kv, None, meta)
     assert_close(out, ref, "FlashAttentionImpl decode")
     assert torch.equal(kv.cpu().view(torch.uint8), kv_ref.view(torch.uint8))
+
+
+def test_opt_attention_prefill_fused_write_matches_literal():
+    """A prefill batch with hidden-designated prompts through both forms of OPTAttention:
+    same cache contents bit for bit, same attention output."""
+    from apt_serve_b200.metadata import BlockPool, build_prefill_metadata
+    rng = np.random.default_rng(4)
+    heads, d, bs = 2, 128, 16
+    e = heads * d
+    lens, hid = [30, 17, 64], [True, False, True]
+    nb = 16
+    pool = BlockPool(nb, rng)
+    tables = [pool.table_for(s, bs, u) for s, u in zip(lens, hid)]
+    meta = A.FlashAttentionMetadata.from_prefill(build_prefill_metadata(lens, hid, tables, bs).to("cuda"))
+    g = torch.Generator(device="cuda").manual_seed(2)
+    hs = torch.randn(sum(lens), e, generator=g, device="cuda", dtype=torch.float16)
+    w = (torch.randn(3 * e, e, generator=g, device="cuda") * 0.05).half()
+    b = torch.randn(3 * e, generator=g, device="cuda").half()
+    wo = (torch.randn(e, e, generator=g, device="cuda") * 0.05).half()
+    bo = torch.randn(e, generator=g, device="cuda").half()
+    outs, caches = [], []
+    for fused in (True, False):
+        layer = OPTAttention(e, heads, w, b, wo, bo, fused=fused)
+        cache = torch.zeros(2, nb, bs, heads, d, device="cuda", dtype=torch.float16)
+        outs.append(layer(hs, cache, None, meta))
+        caches.append(cache)
+    assert torch.equal(caches[0], caches[1])
+    assert caches[0].abs().sum() > 0
+    assert_close(outs[0], outs[1].float(), "prefill output", 1e-3, 1e-3)

@@ -202,3 +202,42 @@ def test_full_size_prefill_write_roundtrip():
     total = cache.double().abs().sum()
     want = x[hid_rows].double().abs().sum() + k[kv_rows].double().abs().sum() + v[kv_rows].double().abs().sum()
     assert torch.allclose(total, want, rtol=1e-9)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_prefill_cache_write_one_launch(dtype):
+    """The fused prefill write against the oracle's two ops (hidden rows + K/V rows of the
+    K/V-designated tokens), bit-exact, including tokens with a padded slot."""
+    nb, bs, h, d = 20, 16, 3, 64
+    pool = BlockPool(nb, np.random.default_rng(1))
+    lens, hid = [20, 9, 33, 50, 1], [True, False, True, False, True]
+    tables = [pool.table_for(s, bs, u) for s, u in zip(lens, hid)]
+    m = build_prefill_metadata(lens, hid, tables, bs)
+    t = sum(lens)
+    x = rand(t, h * d, dtype=dtype, seed=1)
+    qkv = rand(t, 3 * h * d, dtype=dtype, seed=2)          # K and V are column slices of a fused output
+    _, k, v = qkv.chunk(3, dim=-1)
+    cache = rand(2, nb, bs, h, d, dtype=dtype, seed=3)
+    slot_mapping = m.slot_mapping.clone()
+    slot_mapping[[2, 25]] = -1
+    ref = cache.clone()
+    O.hidden_to_cache(x, ref, slot_mapping, m.hidden_cache_use_input, m.hidden_cache_store_tot)
+    O.reshape_and_cache_flash(k.reshape(t, h, d)[m.kv_cache_use_tot], v.reshape(t, h, d)[m.kv_cache_use_tot],
+                              ref[0], ref[1], slot_mapping[m.kv_cache_use_tot])
+    cache_d, qkv_d = cache.cuda(), qkv.cuda()
+    _, k_d, v_d = qkv_d.chunk(3, dim=-1)
+    ops.prefill_cache_write(k_d.view(t, h, d), v_d.view(t, h, d), x.cuda(), cache_d, cache_d,
+                            slot_mapping.cuda(), m.kv_cache_use_tot.cuda(), m.hidden_cache_use_input.cuda())
+    assert torch.equal(bits(cache_d), bits(ref))
+    assert not torch.equal(bits(ref), bits(cache))
+    # only hidden-designated, only K/V-designated, and empty batches
+    for kv_idx, hid_idx in ((m.kv_cache_use_tot[:0], m.hidden_cache_use_input),
+                            (m.kv_cache_use_tot, m.hidden_cache_use_input[:0]),
+                            (m.kv_cache_use_tot[:0], m.hidden_cache_use_input[:0])):
+        c2, r2 = cache.cuda(), cache.clone()
+        O.hidden_to_cache(x, r2, slot_mapping, hid_idx, hid_idx)
+        O.reshape_and_cache_flash(k.reshape(t, h, d)[kv_idx], v.reshape(t, h, d)[kv_idx], r2[0], r2[1],
+                                  slot_mapping[kv_idx])
+        ops.prefill_cache_write(k_d.view(t, h, d), v_d.view(t, h, d), x.cuda(), c2, c2,
+                                slot_mapping.cuda(), kv_idx.cuda(), hid_idx.cuda())
+        assert torch.equal(bits(c2), bits(r2))
