@@ -189,7 +189,7 @@ int aps_paged_decode_attention(void* out, const void* query, const void* key_cac
  *  - No cudaMalloc, cudaFree or allocating library call is made.
  *  - A batch whose scratch need (aps_attention_workspace_bytes of its shape)
  *    exceeds 32 MiB is rejected with APS_ERR_WORKSPACE; e.g. 64 requests x 2048
- *    tokens at 40 heads x 128 need 21 MiB and fit, 256 such requests do not.
+ *    tokens at 40 heads x 128 need about 23 MiB and fit, 256 such requests do not.
  *  - The first call on each device looks up the array's device address
  *    (cudaGetSymbolAddress, with that device current); make that first call
  *    before any stream capture begins.
