@@ -32,7 +32,7 @@ enum PlanWord {
 struct WorkspaceLayout {
   int batch, heads, head_size, max_chunks;  // max_chunks = batch * chunks per longest request
   size_t off_plan, off_part_offset, off_kv_chunks, off_hid_tiles, off_first_tile, off_hid_subs,
-      off_ml, off_acc, total;
+      off_hid_rows, off_ml, off_acc, total;
 };
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
@@ -55,6 +55,7 @@ inline WorkspaceLayout workspace_layout(int batch, int max_blocks_per_seq, int b
   w.off_hid_tiles = o;   o = align_up(o + (size_t)mc * sizeof(int2), 256);
   w.off_first_tile = o;  o = align_up(o + (size_t)(batch + 1) * sizeof(int), 256);
   w.off_hid_subs = o;    o = align_up(o + (size_t)subs * sizeof(int2), 256);
+  w.off_hid_rows = o;    o = align_up(o + (size_t)subs * sizeof(int), 256);
   w.off_ml = o;          o = align_up(o + (size_t)mc * heads * 2 * sizeof(float), 256);
   w.off_acc = o;         o = align_up(o + (size_t)mc * heads * head_size * sizeof(float), 256);
   w.total = o;
@@ -68,6 +69,7 @@ struct WorkspacePtrs {
   int2* hid_tiles;    // (request, chunk) of hidden-cached requests, request order (unpacked plan only)
   int* first_tile;    // [batch] first M tile a hidden request has rows in
   int2* hid_subs;     // per 16-row sub-block of the M tiles: (request, first token) or (-1, 0) padding
+  int* hid_rows;      // per sub-block: first row in the hidden cache (through the block table)
   float* part_ml;     // [slot][head][2]
   float* part_acc;    // [slot][head][head_size]
 };
@@ -81,6 +83,7 @@ inline WorkspacePtrs workspace_ptrs(void* base, const WorkspaceLayout& w) {
   p.hid_tiles = reinterpret_cast<int2*>(b + w.off_hid_tiles);
   p.first_tile = reinterpret_cast<int*>(b + w.off_first_tile);
   p.hid_subs = reinterpret_cast<int2*>(b + w.off_hid_subs);
+  p.hid_rows = reinterpret_cast<int*>(b + w.off_hid_rows);
   p.part_ml = reinterpret_cast<float*>(b + w.off_ml);
   p.part_acc = reinterpret_cast<float*>(b + w.off_acc);
   return p;
@@ -100,8 +103,8 @@ struct AttnShape {
 // the sub-blocks of consecutive hidden requests are packed back to back, so a tile can hold
 // rows of several requests and only the last tile is partly empty.
 int launch_plan(const WorkspacePtrs& ws, const int32_t* seq_lens, const int32_t* cache_type,
-                int batch, int max_blocks_per_seq, int block_size, bool pack_tiles,
-                cudaStream_t stream);
+                const int32_t* block_tables, int batch, int max_blocks_per_seq, int block_size,
+                bool pack_tiles, cudaStream_t stream);
 
 int launch_kv_attention(const WorkspacePtrs& ws, const void* query, const void* key_cache,
                         const void* value_cache, const int32_t* block_tables,

@@ -257,6 +257,7 @@ struct HiddenParams {
   const int* part_offset;
   const int2* hid_subs;       // per 16-row sub-block of the M tiles: (request, first token) / (-1, 0)
   const int* first_tile;      // [batch] first M tile a hidden request has rows in
+  const int* hid_rows;        // per sub-block: its first row in the hidden cache
   float* part_ml;
   float* part_acc;
   const void* query;
@@ -338,12 +339,8 @@ __device__ __forceinline__ void tile_sub_rows(const HiddenParams& p, int tile, i
   if (MODE == kModeAttend) {
 #pragma unroll
     for (int j = 0; j < kSubsPerTile; ++j) {
-      sub_row[j] = 0;
-      if (j < n_sub) {
-        const int2 rec = p.hid_subs[(int64_t)tile * kSubsPerTile + j];   // (request, first token)
-        const int32_t* bt = p.block_tables + (int64_t)rec.x * p.max_blocks_per_seq;
-        sub_row[j] = bt[rec.y / p.block_size] * p.block_size + rec.y % p.block_size;
-      }
+      // resolved through the block tables by the plan kernel
+      sub_row[j] = j < n_sub ? p.hid_rows[(int64_t)tile * kSubsPerTile + j] : 0;
     }
   } else {
 #pragma unroll
@@ -1082,7 +1079,7 @@ extern "C" int aps_hybrid_decode_attention(void* out, const void* query, const v
   // tile per request (what the CUDA-core kernel needs)
   const char* pk = getenv("APS_PACK_TILES");
   const bool pack_tiles = tensor_path && !(pk != nullptr && pk[0] == '0');
-  if ((st = launch_plan(ws, seq_lens, cache_type, batch, max_blocks_per_seq, block_size, pack_tiles, cs)) != APS_OK) return st;
+  if ((st = launch_plan(ws, seq_lens, cache_type, block_tables, batch, max_blocks_per_seq, block_size, pack_tiles, cs)) != APS_OK) return st;
   // K/V requests: on the call's stream before the re-projection kernel.  APS_OVERLAP=1 puts
   // the K/V kernel on a side stream beside the re-projection kernel instead (the combine then
   // waits for both); measured slower (the 4 K/V warps per SM that fit beside the 320-thread
@@ -1104,7 +1101,7 @@ extern "C" int aps_hybrid_decode_attention(void* out, const void* query, const v
     return launch_combine(ws, out, seq_lens, s, cs);
   }
   HiddenParams p{};
-  p.plan = ws.plan; p.part_offset = ws.part_offset; p.hid_subs = ws.hid_subs; p.first_tile = ws.first_tile;
+  p.plan = ws.plan; p.part_offset = ws.part_offset; p.hid_subs = ws.hid_subs; p.first_tile = ws.first_tile; p.hid_rows = ws.hid_rows;
   p.part_ml = ws.part_ml; p.part_acc = ws.part_acc; p.query = query;
   p.block_tables = block_tables; p.seq_lens = seq_lens;
   p.max_blocks_per_seq = max_blocks_per_seq; p.block_size = block_size;

@@ -43,8 +43,9 @@ __device__ __forceinline__ void block_scan2(int* sa, int* sb, int tid, int& a, i
 __global__ void __launch_bounds__(kPlanThreads)
 plan_kernel(int* __restrict__ plan, int* __restrict__ part_offset, int2* __restrict__ kv_chunks,
             int2* __restrict__ hid_tiles, int* __restrict__ first_tile, int2* __restrict__ hid_subs,
-            const int32_t* __restrict__ seq_lens, const int32_t* __restrict__ cache_type, int batch,
-            int max_tokens, int pack_tiles) {
+            int* __restrict__ hid_rows, const int32_t* __restrict__ seq_lens,
+            const int32_t* __restrict__ cache_type, const int32_t* __restrict__ block_tables, int batch,
+            int max_tokens, int max_blocks, int block_size, int pack_tiles) {
   __shared__ int sa[kPlanThreads], sb[kPlanThreads];
   const int tid = threadIdx.x;
   const int per = (batch + kPlanThreads - 1) / kPlanThreads;
@@ -93,8 +94,13 @@ plan_kernel(int* __restrict__ plan, int* __restrict__ part_offset, int2* __restr
     if (hidden(r)) {
       const int n = subs_of(s), real = (s + kSubRowsPlan - 1) / kSubRowsPlan;
       first_tile[r] = g / 8;
-      for (int j = 0; j < n; ++j)
+      for (int j = 0; j < n; ++j) {
         hid_subs[g + j] = j < real ? make_int2(r, j * kSubRowsPlan) : make_int2(-1, 0);
+        const int tok = j * kSubRowsPlan;
+        hid_rows[g + j] = j < real ? block_tables[(int64_t)r * max_blocks + tok / block_size] * block_size +
+                                         tok % block_size
+                                   : 0;
+      }
       if (!pack_tiles)
         for (int c = 0; c < n / 8; ++c) hid_tiles[g / 8 + c] = make_int2(r, c);
       if (real > 0) o_slot += (g + real - 1) / 8 - g / 8 + 1;
@@ -325,11 +331,13 @@ bool kv_attention_supported(int dtype, int head_size) {
 }
 
 int launch_plan(const WorkspacePtrs& ws, const int32_t* seq_lens, const int32_t* cache_type,
-                int batch, int max_blocks_per_seq, int block_size, bool pack_tiles,
-                cudaStream_t stream) {
+                const int32_t* block_tables, int batch, int max_blocks_per_seq, int block_size,
+                bool pack_tiles, cudaStream_t stream) {
   plan_kernel<<<1, kPlanThreads, 0, stream>>>(ws.plan, ws.part_offset, ws.kv_chunks, ws.hid_tiles,
-                                              ws.first_tile, ws.hid_subs, seq_lens, cache_type, batch,
-                                              max_blocks_per_seq * block_size, pack_tiles ? 1 : 0);
+                                              ws.first_tile, ws.hid_subs, ws.hid_rows, seq_lens,
+                                              cache_type, block_tables, batch,
+                                              max_blocks_per_seq * block_size, max_blocks_per_seq,
+                                              block_size, pack_tiles ? 1 : 0);
   return launch_status("plan_kernel");
 }
 
@@ -425,7 +433,7 @@ extern "C" int aps_paged_decode_attention(void* out, const void* query, const vo
   const WorkspaceLayout w = workspace_layout(batch, max_blocks_per_seq, block_size, num_heads, head_size);
   const WorkspacePtrs ws = workspace_ptrs(workspace, w);
   cudaStream_t cs = (cudaStream_t)stream;
-  if ((st = launch_plan(ws, seq_lens, nullptr, batch, max_blocks_per_seq, block_size, false, cs)) != APS_OK) return st;
+  if ((st = launch_plan(ws, seq_lens, nullptr, block_tables, batch, max_blocks_per_seq, block_size, false, cs)) != APS_OK) return st;
   if ((st = launch_kv_attention(ws, query, key_cache, value_cache, block_tables, seq_lens, s, cs)) != APS_OK) return st;
   return launch_combine(ws, out, seq_lens, s, cs);
 }
@@ -501,7 +509,7 @@ extern "C" int aps_paged_decode_attention_static(void* out, const void* query, c
   // plan_kernel rewrites every word of the scratch header (work counter, status word,
   // list sizes) and every partial that the combine reads is rewritten by this call, so
   // nothing left over from the previous call is ever read
-  if ((st = launch_plan(ws, seq_lens, nullptr, batch, max_blocks_per_seq, block_size, false, cs)) != APS_OK) return st;
+  if ((st = launch_plan(ws, seq_lens, nullptr, block_tables, batch, max_blocks_per_seq, block_size, false, cs)) != APS_OK) return st;
   if ((st = launch_kv_attention(ws, query, key_cache, value_cache, block_tables, seq_lens, s, cs)) != APS_OK) return st;
   return launch_combine(ws, out, seq_lens, s, cs);
 }

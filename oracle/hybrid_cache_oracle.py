@@ -339,3 +339,20 @@ def decode_layer_step(hidden_states, q, new_k, new_v, kv_cache, hidden_cache,
     return hybrid_decode_attention(q, kv_cache, hidden_cache, w_k, b_k, w_v, b_v,
                                    meta.private_block_tables, meta.seq_lens_tensor,
                                    meta.cache_type, scale, round_kv_to, requests)
+
+
+def profit_coefficient_literal(token_counts, seconds, block_size: int) -> float:
+    """The scheduler's profit coefficient as the reference computes it from its timing
+    sweep (aptserve_llm_engine.py:336-346): prepend the origin, floor-divide the token
+    counts by the block size with a minimum of one block for non-empty samples, fit
+    scikit-learn's ``LinearRegression`` and return slope / 5."""
+    import numpy as np
+    from sklearn.linear_model import LinearRegression
+
+    x = np.array([0] + list(token_counts))
+    x = x // block_size
+    x[1:][x[1:] == 0] = 1
+    y = np.array([0] + list(seconds))
+    model = LinearRegression()
+    model.fit(x.reshape(-1, 1), y)
+    return float(model.coef_[0] / 5)

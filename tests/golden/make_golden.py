@@ -40,8 +40,10 @@ def build():
         "new_token_slots": new_slots.numpy(),
         "attention_output": out.numpy().astype(np.float32),
         # checksums: the cache before the step, after it, and the rows the step wrote
-        "cache_sum_before": np.float64(w.kv_cache.double().sum().item()),
-        "cache_sum_after": np.float64(cache.double().sum().item()),
+        # (sums of magnitudes: the K/V blocks hold CPU matrix products, whose last bits depend
+        # on the machine's BLAS, so the tests compare these to 1e-6 and not bit for bit)
+        "cache_sum_before": np.float64(w.kv_cache.double().abs().sum().item()),
+        "cache_sum_after": np.float64(cache.double().abs().sum().item()),
         "written_rows": rows[new_slots[torch.tensor(w.use_hidden)]][:, :8].numpy().astype(np.float32),
     }
 

@@ -17,6 +17,10 @@ def load():
     return np.load(GOLDEN)
 
 
+def magnitude_sum(t: torch.Tensor) -> float:
+    return t.double().abs().sum().item()
+
+
 def test_workload_generator_reproduces_the_golden_batch():
     g = load()
     w = make_config_workload(1, kv_from_projection=True)
@@ -24,7 +28,7 @@ def test_workload_generator_reproduces_the_golden_batch():
     assert np.array_equal(g["use_hidden"], np.asarray(w.use_hidden))
     assert np.array_equal(g["private_block_tables"], w.meta.private_block_tables.numpy())
     assert np.array_equal(g["slot_mapping_head"], w.meta.slot_mapping[:64].numpy())
-    assert np.isclose(float(g["cache_sum_before"]), w.kv_cache.double().sum().item(), rtol=1e-12)
+    assert np.isclose(float(g["cache_sum_before"]), magnitude_sum(w.kv_cache), rtol=1e-6)
 
 
 def test_oracle_reproduces_the_golden_output():
@@ -34,7 +38,7 @@ def test_oracle_reproduces_the_golden_output():
     out = O.decode_layer_step(w.hidden_states, w.query, w.new_key, w.new_value, cache, cache,
                               *w.kv_weights(), w.meta, w.scale)
     assert np.allclose(out.numpy(), g["attention_output"], atol=1e-5, rtol=1e-5)
-    assert np.isclose(float(g["cache_sum_after"]), cache.double().sum().item(), rtol=1e-12)
+    assert np.isclose(float(g["cache_sum_after"]), magnitude_sum(cache), rtol=1e-6)
 
 
 @pytest.mark.gpu
@@ -53,7 +57,13 @@ def test_gpu_layer_step_hits_the_golden_output():
                                     m.private_block_tables, m.seq_lens_tensor, m.cache_type, w.scale)
     torch.cuda.synchronize()
     assert np.allclose(out.cpu().numpy(), g["attention_output"], atol=1e-3, rtol=1e-3)
-    assert np.isclose(float(g["cache_sum_after"]), w.kv_cache.double().sum().item(), rtol=1e-12)
+    assert np.isclose(float(g["cache_sum_after"]), magnitude_sum(w.kv_cache.cpu()), rtol=1e-6)
+    # bit for bit against the oracle's cache writes on this machine's copy of the workload
+    wc = make_config_workload(1, kv_from_projection=True)
+    cache = wc.kv_cache.clone()
+    O.decode_layer_step(wc.hidden_states, wc.query, wc.new_key, wc.new_value, cache, cache,
+                        *wc.kv_weights(), wc.meta, wc.scale)
+    assert torch.equal(w.kv_cache.cpu(), cache)
     new_slots = m.slot_mapping[m.hidden_holder_upd][m.cache_type != 0]
     written = O.flat_rows(w.kv_cache.cpu())[new_slots.cpu()][:, :8].numpy()
     assert np.array_equal(written, g["written_rows"])
