@@ -53,6 +53,11 @@ PROTOTYPES = {
                             [c_int64] * 4 + [c_int, c_void_p, c_void_p]),
     "aps_attention_status": (c_int, [c_void_p, c_void_p, c_void_p]),
     "aps_set_profile_events": (c_int, [c_int, c_void_p, c_void_p]),
+    "aps_tp_unique_id": (c_int, [c_void_p]),
+    "aps_tp_init": (c_int, [c_void_p, c_void_p, c_int, c_int]),
+    "aps_tp_allreduce": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_void_p]),
+    "aps_tp_world_size": (c_int, [c_void_p, c_void_p]),
+    "aps_tp_destroy": (c_int, [c_void_p]),
     "aps_decode_metadata_scratch_bytes": (c_size_t, [c_int]),
     "aps_expand_decode_metadata": (c_int, [c_void_p] * 4 + [c_int] * 3 + [c_void_p] * 8 +
                                    [c_int64, c_int64, c_void_p, c_void_p, c_size_t, c_void_p]),

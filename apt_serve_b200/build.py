@@ -16,7 +16,8 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB_DIR = PKG / "lib"
 LIB_PATH = LIB_DIR / "libaptserve_b200.so"
-SOURCES = ["c_api.cu", "cache_ops.cu", "paged_attention.cu", "hybrid_attention.cu", "hidden_simt.cu", "metadata_ops.cu"]
+SOURCES = ["c_api.cu", "cache_ops.cu", "paged_attention.cu", "hybrid_attention.cu", "hidden_simt.cu", "metadata_ops.cu",
+           "tp_comm.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-cudart", "shared"]
 
@@ -59,7 +60,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         if p.returncode != 0:
             raise RuntimeError(f"nvcc failed on {src}:\n{out}")
     tmp = LIB_PATH.with_suffix(".so.tmp")
-    link = [_nvcc(), "-shared", "-cudart", "shared", "-o", str(tmp), *objs]
+    link = [_nvcc(), "-shared", "-cudart", "shared", "-o", str(tmp), *objs, "-ldl"]
     r = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}")

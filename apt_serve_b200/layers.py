@@ -22,7 +22,12 @@ from .metadata import derive_private_block_tables
 
 def tensor_model_parallel_all_reduce(x: torch.Tensor, group=None) -> torch.Tensor:
     """Sum over the tensor-parallel group (the call at aptserve_linear.py:828-829).
-    A no-op without an initialised process group or with a single rank."""
+    A no-op without an initialised process group or with a single rank.  Goes through
+    the library's own communicator (``tp_comm.install``) when one is installed."""
+    from . import tp_comm
+    comm = tp_comm.installed()
+    if comm is not None and group is None:
+        return x if comm.world_size == 1 else comm.all_reduce(x)
     import torch.distributed as dist
     if not dist.is_available() or not dist.is_initialized():
         return x

@@ -148,11 +148,12 @@ def run_cpu_port(workload_cpu, requests, steps, warmup):
 class LayerStep:
     """Holds one rank's tensors and runs the measured step through the package's public API."""
 
-    def __init__(self, w, tp_group=None):
+    def __init__(self, w, tp_group=None, tp_comm=None):
         from apt_serve_b200 import attention as A
         self.A = A
         self.w = w
         self.tp_group = tp_group
+        self.tp_comm = tp_comm
         m = w.meta
         h, d = w.heads, w.shape.head_dim
         self.h, self.d = h, d
@@ -185,7 +186,10 @@ class LayerStep:
     def o_proj(self, attn_out):
         import torch.distributed as dist
         y = torch.nn.functional.linear(attn_out, self.w.o_weight)
-        dist.all_reduce(y, group=self.tp_group)
+        if self.tp_comm is not None:
+            self.tp_comm.all_reduce(y)          # aps_tp_allreduce: the library's NCCL communicator
+        else:
+            dist.all_reduce(y, group=self.tp_group)
         return y + self.w.o_bias
 
     def prefill_writes(self):
@@ -268,7 +272,12 @@ def run_ours(args):
     w = make_decode_workload(shape, lens, hid, seed, dev, tp_rank=rank, tp_size=tp, **extra)
     work = algorithmic_work(shape, lens, hid, tp)
     B = len(lens)
-    st = LayerStep(w, group)
+    tp_comm = None
+    if tp > 1 and os.environ.get("APS_BENCH_TORCH_ALLREDUCE") is None:
+        # the exchange step through the C ABI (aps_tp_*); torch.distributed only carries the id
+        from apt_serve_b200.tp_comm import TensorParallelComm
+        tp_comm = TensorParallelComm.from_torch_distributed()
+    st = LayerStep(w, group, tp_comm)
     peaks = measured_peaks()
 
     def barrier():
@@ -353,6 +362,8 @@ def run_ours(args):
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
     e2e_s = float(t.item())
 
+    if tp_comm is not None:
+        tp_comm.destroy()
     if rank != 0:
         if tp > 1:
             torch.distributed.destroy_process_group()
@@ -405,6 +416,8 @@ def run_ours(args):
                            "new-token cache writes + hybrid decode attention" +
                            (" + o_proj + all-reduce" if tp > 1 else ""),
                    "parallelism": f"tp{tp}" if tp > 1 else "single GPU",
+                   **({"all_reduce": "aps_tp_allreduce (NCCL)" if tp_comm is not None else "torch.distributed (NCCL)"}
+                      if tp > 1 else {}),
                    "l2": (f"inputs larger than L2: {(work['kv_attention_bytes'] + work['hidden_bytes']) / 1e9:.2f} GB streamed per step"
                           if work['kv_attention_bytes'] + work['hidden_bytes'] > 256e6 else
                           f"working set {(work['kv_attention_bytes'] + work['hidden_bytes']) / 1e6:.1f} MB fits in L2: the number is L2-warm"),

@@ -308,6 +308,32 @@ int aps_expand_decode_metadata(const int32_t* block_tables, const int32_t* block
  */
 int aps_set_profile_events(int which, void* start_event, void* stop_event);
 
+/*
+ * Tensor-parallel exchange: the one collective of the path.  Replaces
+ * vllm.distributed.tensor_model_parallel_all_reduce as RowParallelLinear.forward calls
+ * it on the o_proj output of every layer (lin.py:827-829; the bias is added by the
+ * caller after the reduce, lin.py:833-834).  One process per GPU; the communicator is
+ * created on the calling thread's current CUDA device and wraps one NCCL communicator.
+ * NCCL is resolved at run time from the libnccl.so.2 the process has loaded (or the
+ * system's); if none is found every call returns APS_ERR_UNSUPPORTED.
+ *
+ *  aps_tp_unique_id   rank 0 fills `unique_id_out` (APS_TP_UNIQUE_ID_BYTES host bytes)
+ *                     and hands the bytes to the other ranks over the host's own channel
+ *                     (the reference has torch.distributed / Ray for that).
+ *  aps_tp_init        collective over all ranks: every rank passes the same id, its
+ *                     rank and the world size; blocks until all have joined.
+ *  aps_tp_allreduce   in-place sum of `count` elements of `dtype` at `buffer` (device
+ *                     memory), enqueued on `stream`; returns without synchronising.
+ *  aps_tp_world_size  number of ranks of the communicator.
+ *  aps_tp_destroy     releases the communicator (NULL is accepted).
+ */
+#define APS_TP_UNIQUE_ID_BYTES 128
+int aps_tp_unique_id(void* unique_id_out);
+int aps_tp_init(void** comm_out, const void* unique_id, int rank, int world_size);
+int aps_tp_allreduce(void* comm, void* buffer, int64_t count, int dtype, void* stream);
+int aps_tp_world_size(void* comm, int* world_size_out);
+int aps_tp_destroy(void* comm);
+
 #ifdef __cplusplus
 }
 #endif
