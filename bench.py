@@ -20,6 +20,7 @@ import os
 import statistics
 import subprocess
 import sys
+import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -57,29 +58,48 @@ class ClockSampler:
     def __init__(self, gpu_index: int):
         self.gpu_index = gpu_index
         self.proc = None
+        self.lines = []          # (arrival time, text)
+        self.reader = None
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
                  "-lms", "100", "-i", str(self.gpu_index)],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True, bufsize=1)
         except OSError:
             self.proc = None
+            return
 
-    def stop(self):
+        def pump():
+            for line in self.proc.stdout:
+                self.lines.append((time.perf_counter(), line))
+
+        self.reader = threading.Thread(target=pump, daemon=True)
+        self.reader.start()
+
+    def stop(self, t_begin: float, t_end: float):
+        """Summary of the samples that arrived inside ``[t_begin, t_end]`` (the timed
+        region).  A region shorter than the sampling interval may hold none: then the
+        samples of the half second of identical load just before it are used, and
+        ``window`` says so."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.12)
         self.proc.terminate()
         try:
-            out, _ = self.proc.communicate(timeout=5)
+            self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-            out, _ = self.proc.communicate()
+        self.reader.join(timeout=2)
+        inside = [ln for t, ln in self.lines if t_begin <= t <= t_end + 0.02]
+        window = "timed region"
+        if not inside:
+            inside = [ln for t, ln in self.lines if t_begin - 0.5 <= t < t_begin]
+            window = "untimed steps of the same load in the 0.5 s before the timed region (region shorter than the sampling interval)"
         sm, mx, reasons, power = [], [], set(), []
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in out.strip().splitlines():
+        for line in inside:
             f = [x.strip() for x in line.split(",")]
             if len(f) < 9:
                 continue
@@ -93,7 +113,7 @@ class ClockSampler:
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
-                "samples": len(sm), "power_w_max": max(power) if power else None}
+                "samples": len(sm), "power_w_max": max(power) if power else None, "window": window}
 
 
 def dist_env():
@@ -287,9 +307,12 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     # ---- device-resident timing: warm-up, then exactly K steps ----
+    barrier()
+    t_w = time.perf_counter()
     for _ in range(max(args.warmup, 3)):
         st.step()
     barrier()
+    warm_step_s = (time.perf_counter() - t_w) / max(args.warmup, 3)
     K = args.steps
     ev_kv = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
     ev_hid = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
@@ -299,7 +322,15 @@ def run_ours(args):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    # untimed steps of the same load while nvidia-smi comes up (half a second; the count is
+    # rank 0's so that every rank runs the same number of collectives)
+    n_pre = torch.tensor([min(5000, max(1, int(0.5 / max(warm_step_s, 1e-5))))], device=dev)
+    if tp > 1:
+        torch.distributed.broadcast(n_pre, src=0)
+    for _ in range(int(n_pre.item())):
+        st.step()
     barrier()
+    t_region0 = time.perf_counter()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     lib = N.lib()
     ev_pf = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
@@ -311,10 +342,11 @@ def run_ours(args):
         st.step()
     e1.record()
     barrier()
+    t_region1 = time.perf_counter()
     st.prefill_events = None
     lib.aps_set_profile_events(0, None, None)
     lib.aps_set_profile_events(1, None, None)
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(t_region0, t_region1) if rank == 0 else None
     ms_total = e0.elapsed_time(e1)
     t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
     if tp > 1:
