@@ -319,3 +319,48 @@ def test_opt_attention_prefill_fused_write_matches_literal():
     assert torch.equal(caches[0], caches[1])
     assert caches[0].abs().sum() > 0
     assert_close(outs[0], outs[1].float(), "prefill output", 1e-3, 1e-3)
+
+
+# --------------------------------------------------------------------------- #
+# seeded sweep over ragged batch compositions (tile packing, segments, edges)
+# --------------------------------------------------------------------------- #
+EDGE_LENS = (1, 2, 15, 16, 17, 31, 32, 33, 47, 48, 127, 128, 129, 143, 144, 145, 255, 256, 257, 511, 513)
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_hybrid_ragged_batches_sweep(seed):
+    """Random batches whose lengths sit on and next to the 16-token block and 128-row tile
+    boundaries, so that requests share tiles, span tiles and end exactly on their edges;
+    cache types, head counts, dtype and batch size vary with the seed."""
+    rng = np.random.default_rng(7000 + seed)
+    batch = int(rng.integers(1, 28))
+    lens = [int(rng.choice(EDGE_LENS)) if rng.random() < 0.7 else int(rng.integers(1, 700))
+            for _ in range(batch)]
+    mode = seed % 5
+    hidden = ([True] * batch if mode == 0 else [False] * batch if mode == 1
+              else [bool(b) for b in rng.random(batch) < (0.25, 0.5, 0.75)[mode - 2]])
+    heads = int(rng.integers(1, 4))
+    dtype = (torch.float16, torch.bfloat16)[seed % 2]
+    w = small_workload(dtype=dtype, heads=heads, head_dim=128, lens=lens, hidden=hidden, seed=seed)
+    ref = oracle_out(w)
+    dev = w.to("cuda")
+    out = gpu_hybrid(dev)
+    assert_close(out, ref, f"sweep seed {seed}: B={batch} heads={heads} {dtype} lens={lens} hidden={hidden}")
+    again = gpu_hybrid(dev)
+    assert torch.equal(out, again), "two runs on the same inputs differ"
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_hybrid_ragged_batches_sweep_cuda_core_path(seed):
+    """The same sweep on the fp32 CUDA-core re-projection (head sizes 64 and 32)."""
+    rng = np.random.default_rng(7100 + seed)
+    batch = int(rng.integers(1, 12))
+    lens = [int(rng.choice(EDGE_LENS[:16])) if rng.random() < 0.7 else int(rng.integers(1, 300))
+            for _ in range(batch)]
+    hidden = [bool(b) for b in rng.random(batch) < 0.6]
+    head_dim = (64, 32)[seed % 2]
+    w = small_workload(dtype=torch.float32, heads=int(rng.integers(1, 5)), head_dim=head_dim, lens=lens,
+                       hidden=hidden, seed=seed)
+    ref = oracle_out(w)
+    out = gpu_hybrid(w.to("cuda"))
+    assert_close(out, ref, f"fp32 sweep seed {seed}: lens={lens} hidden={hidden}", atol=1e-4, rtol=1e-4)
