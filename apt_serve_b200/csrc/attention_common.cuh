@@ -25,7 +25,8 @@ enum PlanWord {
   kPlanHidCounter = 3,    // reserved
   kPlanStatus = 4,        // non-zero when a kernel gave up on a bounded wait
   kPlanNumHidSubs = 5,    // 16-row sub-blocks in the hidden requests' tile list (incl. padding entries)
-  kPlanStatsWord = 16,    // 8 x 64-bit cycle counters of the re-projection kernel (debug aid)
+  kPlanStatsWord = 16,    // 8 x 64-bit cycle counters of the re-projection kernel (debug aid), then
+                          // one more: SM cycles its CTA 0 spent in the last launch
   kPlanWords = 64
 };
 

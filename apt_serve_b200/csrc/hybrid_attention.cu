@@ -120,6 +120,9 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
+__device__ __forceinline__ void mbar_expect_tx_addr(uint32_t bar_addr, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_addr), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -127,22 +130,25 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_try_wait_addr(uint32_t bar_addr, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+      : "=r"(ok) : "r"(bar_addr), "r"(parity) : "memory");
   return ok != 0;
 }
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  return mbar_try_wait_addr(smem_u32(bar), parity);
+}
 // Bounded wait.  Returns false when it gave up (or another warp already did).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
+__device__ __forceinline__ bool mbar_wait_addr(uint32_t bar_addr, uint32_t parity, volatile int* abort_flag,
+                                               int* status, int code) {
+  if (mbar_try_wait_addr(bar_addr, parity)) return true;
   const long long t0 = clock64();
   int spins = 0;
-  while (!mbar_try_wait(bar, parity)) {
+  while (!mbar_try_wait_addr(bar_addr, parity)) {
     if ((++spins & 255) == 0) {
       if (*abort_flag != 0) return false;
       if (clock64() - t0 > kWaitBudget) {
@@ -153,6 +159,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     }
   }
   return true;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status, int code) {
+  return mbar_wait_addr(smem_u32(bar), parity, abort_flag, status, code);
 }
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -199,6 +209,29 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uin
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// The same with the descriptors given as 32-bit halves (the high half is common to both
+// operands): the issuing thread then steps a descriptor with one 32-bit add.
+template <bool PAIR>
+__device__ __forceinline__ void tc_mma_f16_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi,
+                                              uint32_t idesc, uint32_t accumulate) {
+  if (PAIR)
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate) : "memory");
+  else
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_commit_addr(uint32_t bar_addr) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_addr) : "memory");
 }
 __device__ __forceinline__ void tc_mma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                                 uint32_t idesc, uint32_t accumulate) {
@@ -520,7 +553,7 @@ __device__ __forceinline__ void epilogue_compute(SmemAux* aux, const HiddenParam
 // threads in five warps.  Producer 0 (warp 0) posts the stage's byte count and issues the
 // W boxes; producers 1..4 (warps 6..9) issue two cache blocks of the tile each.  Every
 // producer waits for the stage to be free on its own.
-template <typename T, int MODE, bool PAIR>
+template <typename T, int MODE, bool PAIR, bool STATS>
 __device__ __forceinline__ void tma_producer(const HiddenParams& p, SmemAux* aux, uint8_t* smem,
                                              const CUtensorMap& map_x, const CUtensorMap& map_wk,
                                              const CUtensorMap& map_wv, int prod, int n_tiles,
@@ -537,7 +570,7 @@ __device__ __forceinline__ void tma_producer(const HiddenParams& p, SmemAux* aux
   uint32_t stage = 0, phase = 0;
   bool ok = true;
   long long w_empty = 0, w_issue = 0;
-  const long long p_begin = (p.stats && prod == 0) ? clock64() : 0;
+  const long long p_begin = (STATS && p.stats && prod == 0) ? clock64() : 0;
   for (int i = first; i < n_items && ok; i += stride) {
     const Item it = item_of(i, n_units, p.heads, p.raster_units, p.raster_heads);
     const int tile = PAIR ? it.unit * 2 + (int)rank : it.unit;
@@ -569,36 +602,42 @@ __device__ __forceinline__ void tma_producer(const HiddenParams& p, SmemAux* aux
 #pragma unroll
       for (int j = 0; j < kSubsPerTile; ++j) { if (j == j0) r0 = sub_row[j]; if (j == j0 + 1) r1 = sub_row[j]; }
       const bool has0 = !dense && j0 < n_sub, has1 = !dense && j0 + 1 < n_sub;
-      for (int ks = 0; ks < p.k_slabs; ++ks) {
-        const long long t0 = (p.stats && prod == 0) ? clock64() : 0;
-        if (!mbar_wait(&aux->empty[stage], phase ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
-        const long long t1 = (p.stats && prod == 0) ? clock64() : 0;
-        const uint32_t a_dst = smem_base + stage * kStageBytes;
+      // like the MMA issuer, a producer is one thread with a few hundred cycles per slab:
+      // addresses are stepped, not recomputed from the stage index
+      const uint32_t sub_off = (uint32_t)(j0 * kSubBytes);
+      const uint32_t bar_first = PAIR ? mapa_u32(full_base, 0) : full_base;   // where the bytes are counted
+      const uint32_t empty_base = smem_u32(&aux->empty[0]);
+      uint32_t a_dst = smem_base + stage * kStageBytes, off8 = stage * 8;
+      int x = 0;
+      for (int ks = p.k_slabs; ks > 0; --ks) {
+        const long long t0 = (STATS && p.stats && prod == 0) ? clock64() : 0;
+        if (!mbar_wait_addr(empty_base + off8, phase ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
+        const long long t1 = (STATS && p.stats && prod == 0) ? clock64() : 0;
         const uint32_t b_dst = a_dst + kABytes;
-        const uint32_t bar_local = full_base + stage * 8;
-        const int x = ks * (kBKBytes / (int)sizeof(T));
-        if (post) mbar_expect_tx(&aux->full[stage], tx_bytes);
+        const uint32_t bar = bar_first + off8;
+        if (post) mbar_expect_tx_addr(full_base + off8, tx_bytes);
         if (PAIR) {
-          const uint32_t bar = mapa_u32(bar_local, 0);   // bytes of both CTAs count on the even CTA's barrier
           if (do_dense) tma_load_2d_pair_a(a_dst, &map_x, bar, x, tile * kBM);
-          if (has0) tma_load_2d_pair_a(a_dst + j0 * kSubBytes, &map_x, bar, x, r0);
-          if (has1) tma_load_2d_pair_a(a_dst + (j0 + 1) * kSubBytes, &map_x, bar, x, r1);
+          if (has0) tma_load_2d_pair_a(a_dst + sub_off, &map_x, bar, x, r0);
+          if (has1) tma_load_2d_pair_a(a_dst + sub_off + kSubBytes, &map_x, bar, x, r1);
           if (do_w0) tma_load_2d_pair_a(b_dst, w0_map, bar, x, hrow);
         } else {
-          if (do_dense) tma_load_2d_a(a_dst, &map_x, bar_local, x, tile * kBM);
-          if (has0) tma_load_2d_a(a_dst + j0 * kSubBytes, &map_x, bar_local, x, r0);
-          if (has1) tma_load_2d_a(a_dst + (j0 + 1) * kSubBytes, &map_x, bar_local, x, r1);
-          if (do_w0) tma_load_2d_a(b_dst, w0_map, bar_local, x, hrow);
-          if (do_w1) tma_load_2d_a(b_dst + V::kBBytes / 2, &map_wv, bar_local, x, hrow);
+          if (do_dense) tma_load_2d_a(a_dst, &map_x, bar, x, tile * kBM);
+          if (has0) tma_load_2d_a(a_dst + sub_off, &map_x, bar, x, r0);
+          if (has1) tma_load_2d_a(a_dst + sub_off + kSubBytes, &map_x, bar, x, r1);
+          if (do_w0) tma_load_2d_a(b_dst, w0_map, bar, x, hrow);
+          if (do_w1) tma_load_2d_a(b_dst + V::kBBytes / 2, &map_wv, bar, x, hrow);
         }
-        if (p.stats && prod == 0) { w_empty += t1 - t0; w_issue += clock64() - t1; }
-        if (++stage == kStages) { stage = 0; phase ^= 1; }
+        if (STATS && p.stats && prod == 0) { w_empty += t1 - t0; w_issue += clock64() - t1; }
+        x += kBKBytes / (int)sizeof(T);
+        a_dst += kStageBytes; off8 += 8;
+        if (++stage == kStages) { stage = 0; phase ^= 1; a_dst = smem_base; off8 = 0; }
       }
     } else {
       for (int ks = 0; ks < p.k_slabs; ++ks) {
-        const long long t0 = (p.stats && prod == 0) ? clock64() : 0;
+        const long long t0 = (STATS && p.stats && prod == 0) ? clock64() : 0;
         if (!mbar_wait(&aux->empty[stage], phase ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
-        const long long t1 = (p.stats && prod == 0) ? clock64() : 0;
+        const long long t1 = (STATS && p.stats && prod == 0) ? clock64() : 0;
         const uint32_t a_dst = smem_base + stage * kStageBytes;
         const uint32_t b_dst = a_dst + kABytes;
         const uint32_t bar_local = full_base + stage * 8;
@@ -623,7 +662,7 @@ __device__ __forceinline__ void tma_producer(const HiddenParams& p, SmemAux* aux
           if (do_w0) tma_load_2d_a(b_dst, w0_map, bar_local, x, hrow);
           if (do_w1) tma_load_2d_a(b_dst + V::kBBytes / 2, &map_wv, bar_local, x, hrow);
         }
-        if (p.stats && prod == 0) { w_empty += t1 - t0; w_issue += clock64() - t1; }
+        if (STATS && p.stats && prod == 0) { w_empty += t1 - t0; w_issue += clock64() - t1; }
         if (++stage == kStages) { stage = 0; phase ^= 1; }
       }
     }
@@ -634,7 +673,7 @@ __device__ __forceinline__ void tma_producer(const HiddenParams& p, SmemAux* aux
     const long long t0 = clock64();
     while (clock64() - t0 < 2000000LL) { }
   }
-  if (p.stats && prod == 0) {
+  if (STATS && p.stats && prod == 0) {
     atomicAdd(p.stats + 3, (unsigned long long)w_empty);
     atomicAdd(p.stats + 4, (unsigned long long)(clock64() - p_begin));
     atomicAdd(p.stats + 5, (unsigned long long)w_issue);
@@ -642,7 +681,7 @@ __device__ __forceinline__ void tma_producer(const HiddenParams& p, SmemAux* aux
 }
 
 // ---- the kernel ---------------------------------------------------------------------
-template <typename T, int MODE, bool PAIR>
+template <typename T, int MODE, bool PAIR, bool STATS>
 __global__ void __launch_bounds__(kThreads, 1)
 hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_wk,
                    const __grid_constant__ CUtensorMap map_wv, const HiddenParams p) {
@@ -654,6 +693,7 @@ hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   SmemAux* aux = reinterpret_cast<SmemAux*>(smem + (size_t)kStages * kStageBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long kernel_begin = clock64();
   volatile int* abort_flag = &aux->abort_flag;
   const uint32_t rank = PAIR ? cluster_ctarank() : 0u;   // position in the CTA pair
   const bool leader = rank == 0;
@@ -695,17 +735,28 @@ hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
   if (warp == 0) {
     // ===================== TMA producer 0 =====================
     if (lane == 0)
-      tma_producer<T, MODE, PAIR>(p, aux, smem, map_x, map_wk, map_wv, 0, n_tiles, n_units, n_items,
+      tma_producer<T, MODE, PAIR, STATS>(p, aux, smem, map_x, map_wk, map_wv, 0, n_tiles, n_units, n_items,
                                   first, stride, rank);
     __syncwarp();
   } else if (warp == 1) {
     // ===================== MMA issuer (the even CTA of a pair issues for both) =====================
     if (lane == 0 && leader) {
+      // One lone thread issues an instruction only every few cycles, and it has 512 cycles
+      // per slab: everything the loop needs is a 32-bit register stepped by a constant
+      // (barrier addresses, the low halves of the two operand descriptors), nothing is
+      // recomputed from the stage index, and the cycle counters are compiled out unless asked for.
       const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
       const uint32_t idesc = instr_desc(fmt, PAIR ? 256u : 128u);
-      uint32_t stage = 0, phase = 0, n_local = 0;
+      constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);   // see smem_desc_sw128
+      constexpr uint32_t kDescStep = (uint32_t)kStageBytes >> 4, kDescB = (uint32_t)kABytes >> 4;
+      const uint32_t a_lo_first = ((smem_u32(smem) & 0x3FFFFu) >> 4) | (1u << 16);
+      const uint32_t a_lo_end = a_lo_first + kStages * kDescStep;
+      const uint32_t full_first = smem_u32(&aux->full[0]), full_end = full_first + kStages * 8;
+      const uint32_t empty_own = PAIR ? mapa_u32(smem_u32(&aux->empty[0]), 0) : smem_u32(&aux->empty[0]);
+      const uint32_t peer_delta = PAIR ? mapa_u32(smem_u32(&aux->empty[0]), 1) - empty_own : 0u;
+      uint32_t a_lo = a_lo_first, full_addr = full_first, empty_addr = empty_own, phase = 0, n_local = 0;
       bool ok = true;
-      const bool st = p.stats != nullptr;
+      const bool st = STATS && p.stats != nullptr;
       long long t_begin = st ? clock64() : 0, w_full = 0, w_acc = 0, w_first = 0;
       for (int i = first; i < n_items && ok; i += stride, ++n_local) {
         const uint32_t buf = n_local & 1u, use = n_local >> 1;
@@ -714,32 +765,28 @@ hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         if (st) w_acc += clock64() - t0;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * kBN;
-        for (int ks = 0; ks < p.k_slabs; ++ks) {
-          t0 = st ? clock64() : 0;
-          if (!mbar_wait(&aux->full[stage], phase, abort_flag, p.status, 3)) { ok = false; break; }
-          if (st) { const long long dt = clock64() - t0; w_full += dt; if (ks == 0) w_first += dt; }
+        uint32_t accumulate = 0;
+        for (int ks = p.k_slabs; ks > 0; --ks) {
+          if (st) t0 = clock64();
+          if (!mbar_wait_addr(full_addr, phase, abort_flag, p.status, 3)) { ok = false; break; }
+          if (st) { const long long dt = clock64() - t0; w_full += dt; if (ks == p.k_slabs) w_first += dt; }
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(smem + (size_t)stage * kStageBytes);
-          const uint64_t a_desc = smem_desc_sw128(a_addr);
-          const uint64_t b_desc = smem_desc_sw128(a_addr + kABytes);
-#pragma unroll
-          for (int k = 0; k < kBKBytes / 32; ++k) {
-            if (PAIR)
-              tc_mma_f16_pair(d_tmem, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc,
-                              (ks | k) != 0 ? 1u : 0u);
-            else
-              tc_mma_f16(d_tmem, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc,
-                         (ks | k) != 0 ? 1u : 0u);
-          }
+          const uint32_t b_lo = a_lo + kDescB;
+          tc_mma_f16_lo<PAIR>(d_tmem, a_lo, b_lo, kDescHi, idesc, accumulate);
+          tc_mma_f16_lo<PAIR>(d_tmem, a_lo + 2, b_lo + 2, kDescHi, idesc, 1u);
+          tc_mma_f16_lo<PAIR>(d_tmem, a_lo + 4, b_lo + 4, kDescHi, idesc, 1u);
+          tc_mma_f16_lo<PAIR>(d_tmem, a_lo + 6, b_lo + 6, kDescHi, idesc, 1u);
+          accumulate = 1u;
           if (PAIR) {
-            // release the stage in both CTAs
-            const uint32_t e = smem_u32(&aux->empty[stage]);
-            tc_commit_pair(mapa_u32(e, 0));
-            tc_commit_pair(mapa_u32(e, 1));
+            tc_commit_pair(empty_addr);                 // release the stage in both CTAs
+            tc_commit_pair(empty_addr + peer_delta);
           } else {
-            tc_commit(&aux->empty[stage]);
+            tc_commit_addr(empty_addr);
           }
-          if (++stage == kStages) { stage = 0; phase ^= 1; }
+          a_lo += kDescStep; full_addr += 8; empty_addr += 8;
+          if (full_addr == full_end) {
+            a_lo = a_lo_first; full_addr = full_first; empty_addr = empty_own; phase ^= 1u;
+          }
         }
         if (ok) {
           if (PAIR) {
@@ -751,6 +798,7 @@ hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
           }
         }
       }
+      (void)a_lo_end;
       if (st) {
         atomicAdd(p.stats + 0, (unsigned long long)(clock64() - t_begin));
         atomicAdd(p.stats + 1, (unsigned long long)w_full);
@@ -773,7 +821,7 @@ hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
       // TMA mode: warps 6..9 are producers 1..4
       const int prod = warp - 5;   // warps 6..9 -> producers 1..4
       if (prod > 0 && lane == 0)
-        tma_producer<T, MODE, PAIR>(p, aux, smem, map_x, map_wk, map_wv, prod, n_tiles, n_units, n_items,
+        tma_producer<T, MODE, PAIR, STATS>(p, aux, smem, map_x, map_wk, map_wv, prod, n_tiles, n_units, n_items,
                                     first, stride, rank);
       __syncwarp();
     } else {
@@ -830,13 +878,13 @@ hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
       const bool tile_ok = tile < n_tiles;
       const uint32_t buf = n_local & 1u, use = n_local >> 1;
       epilogue_stage_inputs<T, MODE>(aux, p, tile, tile_ok, it.head, et);
-      const long long t0 = (p.stats && et == 0) ? clock64() : 0;
+      const long long t0 = (STATS && p.stats && et == 0) ? clock64() : 0;
       // one lane per warp polls the barrier; the other 124 threads wait in the hardware
       // barrier of epi_all (polling by every thread floods the SM's mbarrier unit and slows
       // the producer / MMA handshake down)
       const bool got = lane != 0 || mbar_wait(&aux->acc_full[buf], use & 1u, abort_flag, p.status, 4);
       if (!epi_all(got)) { ok = false; break; }
-      const long long t1 = (p.stats && et == 0) ? clock64() : 0;
+      const long long t1 = (STATS && p.stats && et == 0) ? clock64() : 0;
       tc_fence_after();
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * kBN;
       uint64_t* acc_empty = &aux->acc_empty[buf];
@@ -855,6 +903,9 @@ hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
 
   tc_fence_before();
   __syncthreads();
+  // SM cycles CTA 0 spent in the kernel (always recorded: two clock reads per launch)
+  if (MODE == kModeAttend && blockIdx.x == 0 && threadIdx.x == 0)
+    reinterpret_cast<unsigned long long*>(p.plan + kPlanStatsWord)[8] = (unsigned long long)(clock64() - kernel_begin);
   if (PAIR) cluster_sync_all();   // nobody leaves while the peer may still read its memory or signal it
   if (warp == 1) {
     tc_fence_after();
@@ -908,14 +959,14 @@ bool use_pair_variant() {
   return true;
 }
 
-template <typename T, int MODE, bool PAIR>
+template <typename T, int MODE, bool PAIR, bool STATS>
 int launch_hidden_variant(const CUtensorMap& mx, const CUtensorMap& mk, const CUtensorMap& mv,
                           const HiddenParams& p, cudaStream_t stream) {
   static int grid_for_device[64] = {0};
   int dev = 0;
   APS_CUDA(cudaGetDevice(&dev));
   APS_REQUIRE(dev >= 0 && dev < 64, APS_ERR_CUDA, "device index %d out of range", dev);
-  auto kernel = hidden_path_kernel<T, MODE, PAIR>;
+  auto kernel = hidden_path_kernel<T, MODE, PAIR, STATS>;
   constexpr size_t smem = smem_bytes<PAIR>();
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(kThreads);
@@ -974,8 +1025,13 @@ int launch_hidden(const CUtensorMap& mx, const CUtensorMap& mk, const CUtensorMa
   p.a_mode = (want_loaders && !p.dense_a && p.x_base != nullptr && p.hidden_mult64) ? 1 : 0;
   const char* si = getenv("APS_SPLIT_ISSUE");
   p.split_issue = (si != nullptr && si[0] == '0') ? 0 : 1;
-  return use_pair_variant() ? launch_hidden_variant<T, MODE, true>(mx, mk, mv, p, stream)
-                            : launch_hidden_variant<T, MODE, false>(mx, mk, mv, p, stream);
+  // the cycle counters are a separate instantiation of the attend kernel
+  if (MODE == kModeAttend && p.stats != nullptr)
+    return use_pair_variant() ? launch_hidden_variant<T, kModeAttend, true, true>(mx, mk, mv, p, stream)
+                              : launch_hidden_variant<T, kModeAttend, false, true>(mx, mk, mv, p, stream);
+  p.stats = nullptr;
+  return use_pair_variant() ? launch_hidden_variant<T, MODE, true, false>(mx, mk, mv, p, stream)
+                            : launch_hidden_variant<T, MODE, false, false>(mx, mk, mv, p, stream);
 }
 
 // Per-device side stream and fork / join events, created on first use, kept until exit.

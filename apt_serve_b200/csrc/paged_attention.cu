@@ -123,7 +123,7 @@ plan_kernel(int* __restrict__ plan, int* __restrict__ part_offset, int2* __restr
     // entries between the last sub-block and the end of the last tile read as padding
     for (int j = total_sub; j < (total_sub + 7) / 8 * 8; ++j) hid_subs[j] = make_int2(-1, 0);
   }
-  if (tid >= kPlanStatsWord && tid < kPlanStatsWord + 16) plan[tid] = 0;  // optional kernel counters
+  if (tid >= kPlanStatsWord && tid < kPlanStatsWord + 18) plan[tid] = 0;  // optional kernel counters
 }
 
 // ---- K/V streaming ---------------------------------------------------------------
