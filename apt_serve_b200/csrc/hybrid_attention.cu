@@ -164,6 +164,20 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
                                           int* status, int code) {
   return mbar_wait_addr(smem_u32(bar), parity, abort_flag, status, code);
 }
+// The same for a whole converged warp: every lane tests the barrier once; if that fails
+// lane 0 does the bounded wait and the others take its verdict.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar_addr, uint32_t parity, volatile int* abort_flag,
+                                               int* status, int code, int lane) {
+  if (__all_sync(0xffffffffu, mbar_try_wait_addr(bar_addr, parity))) return true;
+  const bool got = lane != 0 || mbar_wait_addr(bar_addr, parity, abort_flag, status, code);
+  return __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0;
+}
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -692,7 +706,9 @@ hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   SmemAux* aux = reinterpret_cast<SmemAux*>(smem + (size_t)kStages * kStageBytes);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // the warp index is broadcast from lane 0 so that the compiler can tell that the role
+  // branches below are uniform across a warp
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
   const long long kernel_begin = clock64();
   volatile int* abort_flag = &aux->abort_flag;
   const uint32_t rank = PAIR ? cluster_ctarank() : 0u;   // position in the CTA pair
@@ -740,11 +756,14 @@ hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     __syncwarp();
   } else if (warp == 1) {
     // ===================== MMA issuer (the even CTA of a pair issues for both) =====================
-    if (lane == 0 && leader) {
-      // One lone thread issues an instruction only every few cycles, and it has 512 cycles
-      // per slab: everything the loop needs is a 32-bit register stepped by a constant
-      // (barrier addresses, the low halves of the two operand descriptors), nothing is
-      // recomputed from the stage index, and the cycle counters are compiled out unless asked for.
+    if (leader) {
+      // The whole warp runs the loop (waits, address stepping) in step and one elected lane
+      // issues the tensor-core instructions: their operands are then warp-uniform values the
+      // compiler can keep in uniform registers.  The issuer has 512 cycles per slab and a
+      // lone warp issues an instruction only every few cycles, so everything the loop needs
+      // is a 32-bit register stepped by a constant (barrier addresses, the low halves of the
+      // two operand descriptors), nothing is recomputed from the stage index, and the cycle
+      // counters are compiled out unless asked for.
       const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
       const uint32_t idesc = instr_desc(fmt, PAIR ? 256u : 128u);
       constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);   // see smem_desc_sw128
@@ -761,34 +780,37 @@ hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
       for (int i = first; i < n_items && ok; i += stride, ++n_local) {
         const uint32_t buf = n_local & 1u, use = n_local >> 1;
         long long t0 = st ? clock64() : 0;
-        if (!mbar_wait(&aux->acc_empty[buf], (use & 1u) ^ 1u, abort_flag, p.status, 2)) { ok = false; break; }
+        if (!mbar_wait_warp(smem_u32(&aux->acc_empty[buf]), (use & 1u) ^ 1u, abort_flag, p.status, 2, lane)) { ok = false; break; }
         if (st) w_acc += clock64() - t0;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * kBN;
         uint32_t accumulate = 0;
         for (int ks = p.k_slabs; ks > 0; --ks) {
           if (st) t0 = clock64();
-          if (!mbar_wait_addr(full_addr, phase, abort_flag, p.status, 3)) { ok = false; break; }
+          if (!mbar_wait_warp(full_addr, phase, abort_flag, p.status, 3, lane)) { ok = false; break; }
           if (st) { const long long dt = clock64() - t0; w_full += dt; if (ks == p.k_slabs) w_first += dt; }
           tc_fence_after();
-          const uint32_t b_lo = a_lo + kDescB;
-          tc_mma_f16_lo<PAIR>(d_tmem, a_lo, b_lo, kDescHi, idesc, accumulate);
-          tc_mma_f16_lo<PAIR>(d_tmem, a_lo + 2, b_lo + 2, kDescHi, idesc, 1u);
-          tc_mma_f16_lo<PAIR>(d_tmem, a_lo + 4, b_lo + 4, kDescHi, idesc, 1u);
-          tc_mma_f16_lo<PAIR>(d_tmem, a_lo + 6, b_lo + 6, kDescHi, idesc, 1u);
-          accumulate = 1u;
-          if (PAIR) {
-            tc_commit_pair(empty_addr);                 // release the stage in both CTAs
-            tc_commit_pair(empty_addr + peer_delta);
-          } else {
-            tc_commit_addr(empty_addr);
+          if (elect_one()) {
+            const uint32_t b_lo = a_lo + kDescB;
+            tc_mma_f16_lo<PAIR>(d_tmem, a_lo, b_lo, kDescHi, idesc, accumulate);
+            tc_mma_f16_lo<PAIR>(d_tmem, a_lo + 2, b_lo + 2, kDescHi, idesc, 1u);
+            tc_mma_f16_lo<PAIR>(d_tmem, a_lo + 4, b_lo + 4, kDescHi, idesc, 1u);
+            tc_mma_f16_lo<PAIR>(d_tmem, a_lo + 6, b_lo + 6, kDescHi, idesc, 1u);
+            if (PAIR) {
+              tc_commit_pair(empty_addr);                 // release the stage in both CTAs
+              tc_commit_pair(empty_addr + peer_delta);
+            } else {
+              tc_commit_addr(empty_addr);
+            }
           }
+          __syncwarp();
+          accumulate = 1u;
           a_lo += kDescStep; full_addr += 8; empty_addr += 8;
           if (full_addr == full_end) {
             a_lo = a_lo_first; full_addr = full_first; empty_addr = empty_own; phase ^= 1u;
           }
         }
-        if (ok) {
+        if (ok && elect_one()) {
           if (PAIR) {
             const uint32_t f = smem_u32(&aux->acc_full[buf]);
             tc_commit_pair(mapa_u32(f, 0));
@@ -797,9 +819,10 @@ hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             tc_commit(&aux->acc_full[buf]);
           }
         }
+        __syncwarp();
       }
       (void)a_lo_end;
-      if (st) {
+      if (st && lane == 0) {
         atomicAdd(p.stats + 0, (unsigned long long)(clock64() - t_begin));
         atomicAdd(p.stats + 1, (unsigned long long)w_full);
         atomicAdd(p.stats + 2, (unsigned long long)w_acc);
