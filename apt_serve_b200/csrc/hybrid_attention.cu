@@ -123,6 +123,9 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_expect_tx_addr(uint32_t bar_addr, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_addr), "r"(bytes) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive_addr(uint32_t bar_addr) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_addr) : "memory");
+}
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -634,6 +637,8 @@ __device__ __forceinline__ void tma_producer(const HiddenParams& p, SmemAux* aux
           if (do_dense) tma_load_2d_pair_a(a_dst, &map_x, bar, x, tile * kBM);
           if (has0) tma_load_2d_pair_a(a_dst + sub_off, &map_x, bar, x, r0);
           if (has1) tma_load_2d_pair_a(a_dst + sub_off + kSubBytes, &map_x, bar, x, r1);
+          if (prod != 0) mbar_arrive_addr(full_base + off8);
+          else if (!leader && !mbar_wait_addr(full_base + off8, phase, abort_flag, p.status, 6)) { ok = false; break; }
           if (do_w0) tma_load_2d_pair_a(b_dst, w0_map, bar, x, hrow);
         } else {
           if (do_dense) tma_load_2d_a(a_dst, &map_x, bar, x, tile * kBM);
@@ -641,6 +646,7 @@ __device__ __forceinline__ void tma_producer(const HiddenParams& p, SmemAux* aux
           if (has1) tma_load_2d_a(a_dst + sub_off + kSubBytes, &map_x, bar, x, r1);
           if (do_w0) tma_load_2d_a(b_dst, w0_map, bar, x, hrow);
           if (do_w1) tma_load_2d_a(b_dst + V::kBBytes / 2, &map_wv, bar, x, hrow);
+          if (prod != 0) mbar_arrive_addr(bar);
         }
         if (STATS && p.stats && prod == 0) { w_empty += t1 - t0; w_issue += clock64() - t1; }
         x += kBKBytes / (int)sizeof(T);
@@ -715,9 +721,20 @@ hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
   const bool leader = rank == 0;
 
   if (threadIdx.x == 0) {
-    // full[s]: one arrival from the TMA producer (with the byte count of its boxes), plus one
-    // per loader thread when the hidden rows are brought in by the loader warps
-    const uint32_t full_count = 1u + ((!PAIR && p.a_mode == 1) ? (uint32_t)kLoaderThreads : 0u);
+    // full[s]: one arrival from producer 0 (with the byte count of the stage's boxes), plus
+    // one per loader thread when the hidden rows are brought in by the loader warps, plus one
+    // per slab from each of this CTA's producers 1..4 when the boxes are split.  The last are
+    // what keeps a producer without boxes in this tile in step: a stage cannot fill, be
+    // consumed and be freed again behind the back of a producer that is still waiting for it
+    // (a parity wait that is lapped twice never returns).  In the odd CTA of a pair, whose
+    // bytes are counted on the even CTA's barrier, full[s] takes only those four arrivals and
+    // its producer 0 waits for them before it issues the stage's W box (an arrival on the
+    // peer's barrier per slab and producer costs ~2000 cycles).
+    const bool loaders_on = !PAIR && p.a_mode == 1;
+    const bool split_on = p.split_issue != 0 && !loaders_on;
+    const uint32_t full_count = (PAIR && cluster_ctarank() != 0)
+                                    ? (split_on ? 4u : 1u)
+                                    : 1u + (loaders_on ? (uint32_t)kLoaderThreads : 0u) + (split_on ? 4u : 0u);
     for (int s = 0; s < kStages; ++s) { mbar_init(&aux->full[s], full_count); mbar_init(&aux->empty[s], 1); }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&aux->acc_full[b], 1);
