@@ -322,13 +322,24 @@ def run_ours(args):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    # untimed steps of the same load while nvidia-smi comes up (half a second; the count is
-    # rank 0's so that every rank runs the same number of collectives)
-    n_pre = torch.tensor([min(5000, max(1, int(0.5 / max(warm_step_s, 1e-5))))], device=dev)
+    # untimed steps of the same load while nvidia-smi comes up: chunks of ~50 ms until its first
+    # sample has arrived and half a second has passed (3 s at most); rank 0 decides so that every
+    # rank runs the same number of collectives
+    chunk_t = torch.tensor([min(2000, max(1, int(0.05 / max(warm_step_s, 1e-5))))], device=dev)
     if tp > 1:
-        torch.distributed.broadcast(n_pre, src=0)
-    for _ in range(int(n_pre.item())):
-        st.step()
+        torch.distributed.broadcast(chunk_t, src=0)
+    chunk = int(chunk_t.item())
+    t_pre = time.perf_counter()
+    while True:
+        for _ in range(chunk):
+            st.step()
+        torch.cuda.synchronize()
+        waited = time.perf_counter() - t_pre
+        go_on = torch.tensor([int((waited < 0.5 or not sampler.lines) and waited < 3.0)], device=dev)
+        if tp > 1:
+            torch.distributed.broadcast(go_on, src=0)
+        if not int(go_on.item()):
+            break
     barrier()
     t_region0 = time.perf_counter()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
