@@ -49,6 +49,13 @@ def measured_peaks():
                 "source": "fallback"}
 
 
+# ncu, 16-request OPT-13B case (profiles/hidden_path_kernel_config5_b16_all_hidden.md,
+# profiles/kv_attention_kernel_config5_b16_all_kv.md): dram read + write bytes per launch over the
+# cached tokens of the launch
+HIDDEN_DRAM_BYTES_PER_TOKEN = (3.007744e9 + 17.6e6) / 29088
+KV_DRAM_BYTES_PER_TOKEN = (595.9e6 + 6.6e6) / 29088
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
@@ -412,6 +419,13 @@ def run_ours(args):
             torch.distributed.destroy_process_group()
         return
 
+    # DRAM bytes per launch, from the ncu captures summarised under profiles/ (16-request case of
+    # the same OPT-13B shapes), scaled by the cached tokens a launch processes: both kernels'
+    # traffic grows in proportion to them (hidden rows once plus the W rows re-streamed per
+    # 16-tile group; K/V rows once).  Other shapes: not captured.
+    opt13b = shape.name == "opt-13b" and tp == 1
+    hid_traffic = int(HIDDEN_DRAM_BYTES_PER_TOKEN * work["t_hidden"]) if opt13b else None
+    kv_traffic = int(KV_DRAM_BYTES_PER_TOKEN * work["t_kv"]) if opt13b else None
     tflops = work["reprojection_flops"] / (hid_ms * 1e-3) / 1e12 if hid_ms > 0 and work["t_hidden"] else 0.0
     kv_gbs = work["kv_attention_bytes"] / (kv_ms * 1e-3) / 1e9 if kv_ms > 0 and work["t_kv"] else 0.0
     if work["t_hidden"] > 0:
@@ -421,16 +435,16 @@ def run_ours(args):
                     "frac_of_burst_peak": round(tflops / peaks["tflops_burst"], 4),
                     "peak_source": peaks["source"] + " (sustained bf16 figure: the kernel runs inside a long step)",
                     "ms_per_launch": round(hid_ms, 4), "flops_per_launch": work["reprojection_flops"],
-                    "traffic": None}
+                    "traffic": hid_traffic}
     else:
         roofline = {"kernel": "kv_attention_kernel", "bound": "hbm", "achieved": round(kv_gbs, 1),
                     "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(kv_gbs / peaks["hbm_gbs"], 4),
                     "peak_source": peaks["source"], "ms_per_launch": round(kv_ms, 4),
-                    "bytes_per_launch": work["kv_attention_bytes"], "traffic": None}
+                    "bytes_per_launch": work["kv_attention_bytes"], "traffic": kv_traffic}
     roofline_kv = {"kernel": "kv_attention_kernel (K/V streaming)", "bound": "hbm",
                    "achieved": round(kv_gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                    "frac": round(kv_gbs / peaks["hbm_gbs"], 4), "ms_per_launch": round(kv_ms, 4),
-                   "bytes_per_launch": work["kv_attention_bytes"]}
+                   "bytes_per_launch": work["kv_attention_bytes"], "traffic": kv_traffic}
 
     # ---- host-core baseline on a bounded sample (rank 0, N = 1 only) ----
     cpu_baseline = None
@@ -438,12 +452,12 @@ def run_ours(args):
         hd = w.heads * shape.head_dim
         sample = cpu_sample_requests(lens, hid, args.cpu_flops, shape.hidden, hd)
         cpu_w = w.cpu()
-        sec = run_cpu_port(cpu_w, sample, 1, 0)
+        sec = run_cpu_port(cpu_w, sample, 2, 0)
         cpu_baseline = {"value": round(len(sample) / sec, 3), "unit": UNIT, "cores": torch.get_num_threads(),
                         "host_cpus": os.cpu_count(), "kind": "port",
                         "sample": f"{len(sample)} of {B} requests in batch order keeping the hidden/K-V mix "
-                                  f"({sum(lens[r] for r in sample)} cached tokens), one step, "
-                                  f"{sec:.2f} s; tokens/s = sampled requests / time"}
+                                  f"({sum(lens[r] for r in sample)} cached tokens), two steps of "
+                                  f"{sec:.2f} s each; tokens/s = sampled requests / time"}
         del cpu_w
 
     line = {
@@ -529,13 +543,13 @@ def main():
     ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4, 5])
     ap.add_argument("--hidden-fraction", type=float, default=None)
     ap.add_argument("--batch", type=int, default=None, help="override the configuration's request count")
-    ap.add_argument("--cpu-flops", type=float, default=6e12,
+    ap.add_argument("--cpu-flops", type=float, default=2e13,
                     help="re-projection FLOPs of the host-core baseline's sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
-        if args.steps > 3:
-            args.steps = 3  # bounded: each step is seconds of host work
+        # bounded: the host cores do ~2 TFLOP/s, so K steps of the sample stay near two minutes
+        args.cpu_flops = min(args.cpu_flops, 2.4e14 / max(1, args.steps))
         run_reference(args)
     else:
         run_ours(args)
