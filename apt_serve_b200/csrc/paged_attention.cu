@@ -86,31 +86,63 @@ plan_kernel(int* __restrict__ plan, int* __restrict__ part_offset, int2* __restr
   block_scan2(sa, sb, tid, slots_inc, dummy);
   const int total_slots = sa[kPlanThreads - 1];
   int o_slot = slots_inc - slots;
-  // write-out
+  // write-out.  The per-request words are written by the request's owner thread; the lists
+  // (one entry per K/V chunk or per 16-row sub-block, up to 128 per request, each sub-block
+  // with a block-table lookup) are filled by the whole CTA: in round k every thread posts its
+  // k-th request in shared memory and warp w fills the lists of entries w, w + 32, ...
+  __shared__ int q_req[kPlanThreads], q_at[kPlanThreads], q_n[kPlanThreads], q_real[kPlanThreads];
+  const int warp = tid >> 5, lane = tid & 31;
   int g = o_sub;
-  for (int r = r0; r < r1; ++r) {
-    const int s = seq_of(r);
-    part_offset[r] = o_slot;
-    if (hidden(r)) {
-      const int n = subs_of(s), real = (s + kSubRowsPlan - 1) / kSubRowsPlan;
-      first_tile[r] = g / 8;
-      for (int j = 0; j < n; ++j) {
-        hid_subs[g + j] = j < real ? make_int2(r, j * kSubRowsPlan) : make_int2(-1, 0);
-        const int tok = j * kSubRowsPlan;
-        hid_rows[g + j] = j < real ? block_tables[(int64_t)r * max_blocks + tok / block_size] * block_size +
-                                         tok % block_size
-                                   : 0;
+  for (int k = 0; k < per; ++k) {
+    const int r = r0 + k;
+    q_n[tid] = 0;
+    if (r < r1) {
+      const int s = seq_of(r);
+      part_offset[r] = o_slot;
+      q_req[tid] = r;
+      if (hidden(r)) {
+        const int n = subs_of(s), real = (s + kSubRowsPlan - 1) / kSubRowsPlan;
+        first_tile[r] = g / 8;
+        q_at[tid] = g; q_n[tid] = n; q_real[tid] = real;
+        if (real > 0) o_slot += (g + real - 1) / 8 - g / 8 + 1;
+        g += n;
+      } else {
+        first_tile[r] = 0;
+        const int c = (s + kChunkTokens - 1) / kChunkTokens;
+        q_at[tid] = o_kv; q_n[tid] = c; q_real[tid] = -1;   // -1 marks a K/V request
+        o_kv += c;
+        o_slot += c;
       }
-      if (!pack_tiles)
-        for (int c = 0; c < n / 8; ++c) hid_tiles[g / 8 + c] = make_int2(r, c);
-      if (real > 0) o_slot += (g + real - 1) / 8 - g / 8 + 1;
-      g += n;
-    } else {
-      first_tile[r] = 0;
-      const int c = (s + kChunkTokens - 1) / kChunkTokens;
-      for (int j = 0; j < c; ++j) kv_chunks[o_kv++] = make_int2(r, j);
-      o_slot += c;
     }
+    __syncthreads();
+    for (int e = warp; e < kPlanThreads; e += kPlanThreads / 32) {
+      const int n = q_n[e];
+      if (n == 0) continue;
+      const int req = q_req[e], at = q_at[e], real = q_real[e];
+      if (real < 0) {
+        for (int j = lane; j < n; j += 32) kv_chunks[at + j] = make_int2(req, j);
+      } else {
+        const int32_t* bt = block_tables + (int64_t)req * max_blocks;
+        for (int j0 = 0; j0 < n; j0 += 128) {
+          int blk[4];   // four independent block-table loads per lane before the stores
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int j = j0 + lane + 32 * u;
+            blk[u] = j < real ? bt[j * kSubRowsPlan / block_size] : 0;
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int j = j0 + lane + 32 * u;
+            if (j >= n) continue;
+            const int tok = j * kSubRowsPlan;
+            hid_subs[at + j] = j < real ? make_int2(req, tok) : make_int2(-1, 0);
+            hid_rows[at + j] = j < real ? blk[u] * block_size + tok % block_size : 0;
+            if (!pack_tiles && (j & 7) == 0) hid_tiles[(at + j) / 8] = make_int2(req, j / 8);
+          }
+        }
+      }
+    }
+    __syncthreads();
   }
   if (tid == kPlanThreads - 1) {
     part_offset[batch] = total_slots;
