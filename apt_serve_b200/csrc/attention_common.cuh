@@ -95,7 +95,6 @@ struct AttnShape {
   int64_t query_stride, out_stride, block_stride;
   float scale;
   int dtype;
-  bool side_by_side = false;   // the K/V kernel shares the SMs with the re-projection kernel
 };
 
 // cache_type may be NULL (all requests K/V-cached).  The M tiles of the hidden requests are

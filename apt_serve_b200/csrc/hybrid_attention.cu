@@ -20,9 +20,10 @@
 //             issue two 16-row boxes (two cache blocks of the tile) each; 128-byte swizzle,
 //             multi-stage ring.  One thread cannot issue ten tensor copies in the 512
 //             cycles the tensor cores need for a slab, hence the split;
-//   warp 1    tcgen05.mma issuer (K = 16 per instruction, 4 per slab); the
-//             accumulator is double-buffered in the 512 TMEM columns, so the main
-//             loop of item i+1 overlaps the epilogue of item i;
+//   warp 1    tcgen05.mma issuer (K = 16 per instruction, 4 per slab): the whole warp
+//             runs the loop in step and one elected lane issues, on warp-uniform
+//             operands; the accumulator is double-buffered in the 512 TMEM columns, so
+//             the main loop of item i+1 overlaps the epilogue of item i;
 //   warps 2-5 epilogue: one thread per token row reads its K row from TMEM, adds
 //             b_k, dots with its request's q (pre-scaled by scale*log2 e); maxima, sums
 //             and the weighted V column sums are formed per 16-row block with half-warp
@@ -42,9 +43,8 @@
 // that hidden tiles and W slabs are shared through L2.
 //
 // Environment knobs (read at call time): APS_HIDDEN_VARIANT=single|pair,
-// APS_RASTER=units,heads, APS_PACK_TILES=0, APS_SPLIT_ISSUE=0, APS_A_MODE=loaders (hidden
-// rows by cp.async loader warps, single variant), APS_STATS=1 (cycle counters in the
-// scratch header), APS_FORCE_SIMT=1, APS_OVERLAP=1, APS_DENSE_A=0.
+// APS_RASTER=units,heads, APS_PACK_TILES=0, APS_SPLIT_ISSUE=0, APS_STATS=1 (cycle counters
+// in the scratch header), APS_FORCE_SIMT=1, APS_DENSE_A=0.
 //
 // Every mbarrier wait is bounded by a clock budget; a wait that runs out records
 // a code in the plan's status word, tells the other warps through shared memory,
@@ -68,8 +68,7 @@ constexpr int kABytes = kBM * kBKBytes;          // 16 KB
 constexpr int kSubRows = 16;                     // rows per TMA box of the hidden cache
 constexpr int kSubBytes = kSubRows * kBKBytes;   // 2 KB
 constexpr int kSubsPerTile = kBM / kSubRows;     // 8
-constexpr int kThreads = 320;          // warps 0-1 TMA / MMA, 2-5 epilogue, 6-9 hidden-row loaders
-constexpr int kLoaderThreads = 128;
+constexpr int kThreads = 320;          // warps 0 and 6-9 TMA producers, 1 MMA issue, 2-5 epilogue
 constexpr int kMaxStages = 6;
 constexpr long long kWaitBudget = 4000000000LL;  // clock cycles (~2 s) before a wait gives up
 
@@ -331,12 +330,7 @@ struct HiddenParams {
   int raster_units;           // units per group of the work order (see item_of)
   int raster_heads;           // heads per group of the work order
   int dense_a;                // X rows of a tile are contiguous: map_x has a 128-row box
-  int a_mode;                 // 0: hidden rows by TMA boxes, 1: by the loader warps (cp.async)
   int split_issue;            // the boxes of a stage are issued by four producer threads
-  int hidden_mult64;          // hidden size is a multiple of 64 elements
-  const void* x_base;         // first row of the hidden cache / X matrix (a_mode 1)
-  int64_t x_row_bytes;        // its row stride in bytes
-  int64_t x_rows;             // number of addressable rows (rows past it read as zeros)
   unsigned long long* stats;  // optional cycle counters (nullptr = off): see aps_hybrid_decode_attention
   int* status;
 };
@@ -581,8 +575,7 @@ __device__ __forceinline__ void tma_producer(const HiddenParams& p, SmemAux* aux
   constexpr int kStageBytes = kABytes + V::kBBytes;
   volatile int* abort_flag = &aux->abort_flag;
   const bool leader = rank == 0;
-  const bool loaders = !PAIR && p.a_mode == 1;   // hidden rows come from the loader warps
-  const bool split = p.split_issue != 0 && !loaders;   // else producer 0 issues everything
+  const bool split = p.split_issue != 0;   // else producer 0 issues everything
   if (!split && prod != 0) return;
   uint32_t stage = 0, phase = 0;
   bool ok = true;
@@ -591,7 +584,7 @@ __device__ __forceinline__ void tma_producer(const HiddenParams& p, SmemAux* aux
   for (int i = first; i < n_items && ok; i += stride) {
     const Item it = item_of(i, n_units, p.heads, p.raster_units, p.raster_heads);
     const int tile = PAIR ? it.unit * 2 + (int)rank : it.unit;
-    const int n_sub = loaders ? 0 : tile_n_sub<MODE>(p, tile, n_tiles);
+    const int n_sub = tile_n_sub<MODE>(p, tile, n_tiles);
     int sub_row[kSubsPerTile];
     tile_sub_rows<MODE>(p, n_sub > 0 ? tile : 0, n_sub, sub_row);
     // a dense X tile is one 128-row box (rows past the end are zero-filled and still
@@ -721,8 +714,7 @@ hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
   const bool leader = rank == 0;
 
   if (threadIdx.x == 0) {
-    // full[s]: one arrival from producer 0 (with the byte count of the stage's boxes), plus
-    // one per loader thread when the hidden rows are brought in by the loader warps, plus one
+    // full[s]: one arrival from producer 0 (with the byte count of the stage's boxes), plus one
     // per slab from each of this CTA's producers 1..4 when the boxes are split.  The last are
     // what keeps a producer without boxes in this tile in step: a stage cannot fill, be
     // consumed and be freed again behind the back of a producer that is still waiting for it
@@ -730,11 +722,9 @@ hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     // bytes are counted on the even CTA's barrier, full[s] takes only those four arrivals and
     // its producer 0 waits for them before it issues the stage's W box (an arrival on the
     // peer's barrier per slab and producer costs ~2000 cycles).
-    const bool loaders_on = !PAIR && p.a_mode == 1;
-    const bool split_on = p.split_issue != 0 && !loaders_on;
-    const uint32_t full_count = (PAIR && cluster_ctarank() != 0)
-                                    ? (split_on ? 4u : 1u)
-                                    : 1u + (loaders_on ? (uint32_t)kLoaderThreads : 0u) + (split_on ? 4u : 0u);
+    const bool split_on = p.split_issue != 0;
+    const uint32_t full_count = (PAIR && cluster_ctarank() != 0) ? (split_on ? 4u : 1u)
+                                                                 : 1u + (split_on ? 4u : 0u);
     for (int s = 0; s < kStages; ++s) { mbar_init(&aux->full[s], full_count); mbar_init(&aux->empty[s], 1); }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&aux->acc_full[b], 1);
@@ -849,63 +839,11 @@ hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     }
     __syncwarp();
   } else if (warp >= 6) {
-    // ===================== hidden-row loaders (warps 6..9) =====================
-    // A TMA box costs the copy engine a fixed ~25 ns whatever its size, and a paged tile
-    // needs eight 16-row boxes per slab, which alone holds the main loop near 60 % of its
-    // dense rate.  So the paged hidden rows are brought in with plain 16-byte asynchronous
-    // copies instead: thread t copies 16-byte column chunk (t % 8) of row (t / 8) of every
-    // cache block of the tile into the 128-byte-swizzled stage (chunk index XOR row % 8),
-    // and the stage's barrier counts one arrival per thread, delivered by the copy unit when
-    // that thread's copies have landed.  The W boxes stay on TMA.
-    if (!(!PAIR && p.a_mode == 1)) {
-      // TMA mode: warps 6..9 are producers 1..4
-      const int prod = warp - 5;   // warps 6..9 -> producers 1..4
-      if (prod > 0 && lane == 0)
-        tma_producer<T, MODE, PAIR, STATS>(p, aux, smem, map_x, map_wk, map_wv, prod, n_tiles, n_units, n_items,
-                                    first, stride, rank);
-      __syncwarp();
-    } else {
-      const int t = (int)threadIdx.x - (kThreads - kLoaderThreads);
-      const int r16 = t >> 3, col = t & 7;
-      const uint32_t swz = (uint32_t)(r16 * kBKBytes + ((col ^ (r16 & 7)) << 4));
-      const char* xb = static_cast<const char*>(p.x_base);
-      uint32_t stage = 0, phase = 0;
-      bool ok = true;
-      for (int i = first; i < n_items && ok; i += stride) {
-        const Item it = item_of(i, n_units, p.heads, p.raster_units, p.raster_heads);
-        const int tile = it.unit;
-        const int n_sub = tile_n_sub<MODE>(p, tile, n_tiles);
-        int sub_row[kSubsPerTile];
-        tile_sub_rows<MODE>(p, n_sub > 0 ? tile : 0, n_sub, sub_row);
-        const char* src[kSubsPerTile];
-        uint32_t in_range = 0;   // bit c: the row of sub-block c exists (else zero-fill)
-#pragma unroll
-        for (int c = 0; c < kSubsPerTile; ++c) {
-          const int64_t row = (int64_t)sub_row[c] + r16;
-          const bool okr = row < p.x_rows;
-          in_range |= (okr ? 1u : 0u) << c;
-          src[c] = xb + (okr ? row : 0) * p.x_row_bytes + col * 16;
-        }
-        for (int ks = 0; ks < p.k_slabs; ++ks) {
-          {
-            const bool got = lane != 0 || mbar_wait(&aux->empty[stage], phase ^ 1, abort_flag, p.status, 5);
-            ok = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0;   // lane 0 polls for the warp
-            if (!ok) break;
-          }
-          const uint32_t dst = smem_u32(smem + (size_t)stage * kStageBytes) + swz;
-#pragma unroll
-          for (int c = 0; c < kSubsPerTile; ++c)
-            if (c < n_sub)
-              asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + c * kSubBytes),
-                           "l"(src[c] + (int64_t)ks * kBKBytes), "r"(((in_range >> c) & 1u) * 16u) : "memory");
-          // arrives on the stage's barrier when this thread's copies above have landed
-          asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&aux->full[stage])) : "memory");
-          if (++stage == kStages) { stage = 0; phase ^= 1; }
-        }
-      }
-      // the copies issued last must land before the CTA's shared memory is released
-      asm volatile("cp.async.wait_all;" ::: "memory");
-    }
+    // ===================== TMA producers 1..4 (warps 6..9) =====================
+    if (lane == 0)
+      tma_producer<T, MODE, PAIR, STATS>(p, aux, smem, map_x, map_wk, map_wv, warp - 5, n_tiles, n_units,
+                                         n_items, first, stride, rank);
+    __syncwarp();
   } else {
     // ===================== epilogue (warps 2..5) =====================
     const int quarter = warp & 3;               // TMEM lanes this warp may read
@@ -1057,12 +995,6 @@ int launch_hidden(const CUtensorMap& mx, const CUtensorMap& mk, const CUtensorMa
                   HiddenParams p, cudaStream_t stream) {
   raster_sizes(&p.raster_units, &p.raster_heads);
   if (p.raster_heads > p.heads) p.raster_heads = p.heads;
-  // hidden rows come in as TMA boxes; APS_A_MODE=loaders (single-CTA variant only) brings
-  // paged rows in with the loader warps instead, which needs a hidden size that is a whole
-  // number of 64-element slabs (TMA zero-fills a ragged tail, plain copies cannot)
-  const char* am = getenv("APS_A_MODE");
-  const bool want_loaders = am != nullptr && strcmp(am, "loaders") == 0;
-  p.a_mode = (want_loaders && !p.dense_a && p.x_base != nullptr && p.hidden_mult64) ? 1 : 0;
   const char* si = getenv("APS_SPLIT_ISSUE");
   p.split_issue = (si != nullptr && si[0] == '0') ? 0 : 1;
   // the cycle counters are a separate instantiation of the attend kernel
@@ -1072,25 +1004,6 @@ int launch_hidden(const CUtensorMap& mx, const CUtensorMap& mk, const CUtensorMa
   p.stats = nullptr;
   return use_pair_variant() ? launch_hidden_variant<T, MODE, true, false>(mx, mk, mv, p, stream)
                             : launch_hidden_variant<T, MODE, false, false>(mx, mk, mv, p, stream);
-}
-
-// Per-device side stream and fork / join events, created on first use, kept until exit.
-struct SideStream { cudaStream_t stream; cudaEvent_t forked, joined; };
-int side_stream(SideStream** out) {
-  static SideStream table[64] = {};
-  int dev = 0;
-  APS_CUDA(cudaGetDevice(&dev));
-  APS_REQUIRE(dev >= 0 && dev < 64, APS_ERR_CUDA, "device index %d out of range", dev);
-  SideStream* s = &table[dev];
-  if (s->stream == nullptr) {
-    cudaStream_t st;
-    APS_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
-    APS_CUDA(cudaEventCreateWithFlags(&s->forked, cudaEventDisableTiming));
-    APS_CUDA(cudaEventCreateWithFlags(&s->joined, cudaEventDisableTiming));
-    s->stream = st;
-  }
-  *out = s;
-  return APS_OK;
 }
 
 struct HiddenArgs {
@@ -1176,17 +1089,8 @@ extern "C" int aps_hybrid_decode_attention(void* out, const void* query, const v
   const char* pk = getenv("APS_PACK_TILES");
   const bool pack_tiles = tensor_path && !(pk != nullptr && pk[0] == '0');
   if ((st = launch_plan(ws, seq_lens, cache_type, block_tables, batch, max_blocks_per_seq, block_size, pack_tiles, cs)) != APS_OK) return st;
-  // K/V requests: on the call's stream before the re-projection kernel.  APS_OVERLAP=1 puts
-  // the K/V kernel on a side stream beside the re-projection kernel instead (the combine then
-  // waits for both); measured slower (the 4 K/V warps per SM that fit beside the 320-thread
-  // re-projection CTA stream at a small fraction of the HBM rate), so it is off by default
-  const char* ov = getenv("APS_OVERLAP");
-  const bool have_kv = key_cache != nullptr && value_cache != nullptr;
-  SideStream* side = nullptr;
-  if (have_kv && tensor_path && ov != nullptr && ov[0] == '1') {
-    if ((st = side_stream(&side)) != APS_OK) return st;
-  }
-  if (have_kv && side == nullptr) {
+  // K/V requests: on the call's stream before the re-projection kernel
+  if (key_cache != nullptr && value_cache != nullptr) {
     if ((st = launch_kv_attention(ws, query, key_cache, value_cache, block_tables, seq_lens, s, cs)) != APS_OK) return st;
   }
   if (!tensor_path) {
@@ -1203,21 +1107,11 @@ extern "C" int aps_hybrid_decode_attention(void* out, const void* query, const v
   p.max_blocks_per_seq = max_blocks_per_seq; p.block_size = block_size;
   p.query_stride = query_stride; p.scale_log2 = scale * 1.4426950408889634f;
   p.b_k = b_k; p.b_v = b_v; p.heads = num_heads; p.k_slabs = (hidden_size + 63) / 64;
-  p.x_base = hidden_cache; p.x_row_bytes = hidden_row_stride * 2; p.x_rows = num_hidden_rows; p.hidden_mult64 = hidden_size % 64 == 0;
   p.status = ws.plan + kPlanStatus;
   p.stats = getenv("APS_STATS") != nullptr ? reinterpret_cast<unsigned long long*>(ws.plan + kPlanStatsWord) : nullptr;
-  if (side != nullptr) APS_CUDA(cudaEventRecord(side->forked, cs));
   st = dtype == APS_BF16 ? launch_hidden<__nv_bfloat16, kModeAttend>(mx, mk, mv, p, cs)
                          : launch_hidden<__half, kModeAttend>(mx, mk, mv, p, cs);
   if (st != APS_OK) return st;
-  if (side != nullptr) {
-    APS_CUDA(cudaStreamWaitEvent(side->stream, side->forked, 0));
-    AttnShape s2 = s;
-    s2.side_by_side = true;
-    if ((st = launch_kv_attention(ws, query, key_cache, value_cache, block_tables, seq_lens, s2, side->stream)) != APS_OK) return st;
-    APS_CUDA(cudaEventRecord(side->joined, side->stream));
-    APS_CUDA(cudaStreamWaitEvent(cs, side->joined, 0));
-  }
   return launch_combine(ws, out, seq_lens, s, cs);
 }
 
@@ -1244,7 +1138,6 @@ extern "C" int aps_kv_reprojection(void* kv, const void* x, const int32_t* block
   p.kv_out = kv; p.block_ids = block_ids; p.n_rows = n_rows; p.kv_stride = kv_stride;
   p.n_store_tiles = (int)((n_rows + kBM - 1) / kBM);
   p.b_k = b_k; p.b_v = b_v; p.heads = num_heads; p.k_slabs = (hidden_size + 63) / 64;
-  p.x_base = x; p.x_row_bytes = x_row_stride * 2; p.x_rows = num_x_rows; p.hidden_mult64 = hidden_size % 64 == 0;
   p.status = status_word;
   cudaStream_t cs = (cudaStream_t)stream;
   return dtype == APS_BF16 ? launch_hidden<__nv_bfloat16, kModeStore>(mx, mk, mv, p, cs)

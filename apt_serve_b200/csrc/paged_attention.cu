@@ -326,10 +326,9 @@ template <typename T, int D>
 int launch_kv_typed(const WorkspacePtrs& ws, const void* query, const void* key_cache,
                     const void* value_cache, const int32_t* block_tables, const int32_t* seq_lens,
                     const AttnShape& s, cudaStream_t stream) {
-  // alone on the GPU: 2 CTAs of 8 warps per SM.  Beside the re-projection kernel (which keeps
-  // one 320-thread CTA and most of the registers on every SM): 1 CTA of 4 warps per SM.
-  const int grid = s.side_by_side ? sm_count() : sm_count() * 2;
-  const int threads = s.side_by_side ? 4 * 32 : kKvWarps * 32;
+  // 2 persistent CTAs of 8 warps per SM
+  const int grid = sm_count() * 2;
+  const int threads = kKvWarps * 32;
   const float scale_log2 = s.scale * 1.4426950408889634f;
   ScopedProfile prof(0, stream);
   kv_attention_kernel<T, D><<<grid, threads, 0, stream>>>(
