@@ -364,3 +364,16 @@ def test_hybrid_ragged_batches_sweep_cuda_core_path(seed):
     ref = oracle_out(w)
     out = gpu_hybrid(w.to("cuda"))
     assert_close(out, ref, f"fp32 sweep seed {seed}: lens={lens} hidden={hidden}", atol=1e-4, rtol=1e-4)
+
+
+def test_more_requests_than_plan_threads():
+    """1300 short requests: the plan kernel's threads own two requests each, so its list
+    filling runs two rounds; K/V and hidden requests alternate in runs of three."""
+    rng = np.random.default_rng(42)
+    batch = 1300
+    lens = [int(v) for v in rng.integers(1, 41, size=batch)]
+    hidden = [(r // 3) % 2 == 0 for r in range(batch)]
+    w = small_workload(dtype=torch.float16, heads=1, head_dim=128, lens=lens, hidden=hidden, seed=9)
+    ref = oracle_out(w)
+    out = gpu_hybrid(w.to("cuda"))
+    assert_close(out, ref, "1300 requests")

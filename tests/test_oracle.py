@@ -141,3 +141,30 @@ def test_config1_runs_end_to_end_on_cpu():
     out = O.decode_layer_step(w.hidden_states, w.query, w.new_key, w.new_value, w.kv_cache,
                               w.hidden_cache, wk, bk, wv, bv, w.meta, w.scale)
     assert out.shape == (8, 768) and torch.isfinite(out).all()
+
+
+def test_projection_absorption_gives_the_same_attention():
+    """The algebra behind the next step noted in the design: for a hidden-cached request
+    softmax(q.(W_k x_t + b_k)) . (W_v x_t + b_v) over t equals W_v (sum_t p_t x_t) + b_v with
+    p = softmax((W_k^T q) . x_t): the bias term of the scores is constant over t."""
+    import torch
+    from helpers import small_workload
+    w = small_workload(dtype=torch.float32, heads=3, head_dim=32, lens=(37, 5, 130), hidden=(True, True, True))
+    wk, bk, wv, bv = w.kv_weights()
+    ref = O.hybrid_decode_attention(w.query, w.kv_cache, w.hidden_cache, wk, bk, wv, bv,
+                                    w.meta.private_block_tables, w.meta.seq_lens_tensor,
+                                    w.meta.cache_type, w.scale)
+    rows = O.flat_rows(w.hidden_cache)
+    h, d = w.heads, w.shape.head_dim
+    bs = w.shape.block_size
+    out = torch.empty_like(ref)
+    for r, s in enumerate(w.seq_lens):
+        pos = torch.arange(s)
+        blk = w.meta.private_block_tables[r, pos // bs].long()
+        x = rows[blk * bs + pos % bs].float()                                   # [s, E]
+        q = w.query[r].view(h, d).float()
+        q_abs = torch.einsum("hd,hde->he", q, wk.float().view(h, d, -1)) * w.scale   # W_k^T q per head
+        p = torch.softmax(x @ q_abs.t(), dim=0)                                  # [s, h]
+        z = p.t() @ x                                                           # [h, E]
+        out[r] = (torch.einsum("he,hde->hd", z, wv.float().view(h, d, -1)) + bv.float().view(h, d)).reshape(-1)
+    assert torch.allclose(out, ref, atol=2e-5, rtol=2e-5)
