@@ -154,6 +154,96 @@ def hybrid_decode_attention(query: torch.Tensor, kv_cache: Optional[torch.Tensor
     return out
 
 
+_absorbed_scratch: Dict[torch.device, Dict[str, torch.Tensor]] = {}
+
+
+def _scratch(dev: torch.device, name: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
+    """A per-device buffer that only grows (the scores / absorbed-query / weighted-sum scratch)."""
+    bufs = _absorbed_scratch.setdefault(dev, {})
+    t = bufs.get(name)
+    if t is None or t.numel() < numel or t.dtype != dtype:
+        t = torch.empty(numel, dtype=dtype, device=dev)
+        bufs[name] = t
+    return t[:numel]
+
+
+def hybrid_decode_attention_absorbed(query: torch.Tensor, kv_cache: Optional[torch.Tensor],
+                                     hidden_cache: torch.Tensor, w_k: torch.Tensor,
+                                     b_k: Optional[torch.Tensor], w_v: torch.Tensor,
+                                     b_v: Optional[torch.Tensor], block_tables: torch.Tensor,
+                                     seq_lens: torch.Tensor, cache_type: torch.Tensor, scale: float,
+                                     hidden_rows: Optional[torch.Tensor] = None,
+                                     num_heads: Optional[int] = None, head_size: Optional[int] = None,
+                                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Hybrid decode attention with the projections of hidden-cached requests absorbed into
+    the query and the output instead of re-projecting every cached row: same arguments and
+    result as ``hybrid_decode_attention`` (``b_k`` cancels in the softmax and is unused).
+
+    ``scores = X (W_k,h^T q)``, ``z = softmax(scores)^T X``, ``out_h = W_v,h z + b_v``: the fold
+    and the unfold are one batched GEMM each (library calls), the two passes over the cached
+    hidden rows are ``aps_absorbed_hidden_attention``.  K/V-cached requests take the K/V
+    streaming path.  ``hidden_rows``: the batch rows of the hidden-cached requests
+    (``hidden_cache_use_input`` of the metadata); derived from ``cache_type`` with a host
+    synchronisation when absent.
+    """
+    dev = N.require_cuda(query, kv_cache, hidden_cache, w_k, w_v, b_v, block_tables, seq_lens, cache_type)
+    b = query.shape[0]
+    if out is None:
+        out = torch.empty_like(query)
+    if b == 0:
+        return out
+    if kv_cache is not None:
+        _, _, bs, h, d = kv_cache.shape
+    else:
+        if num_heads is None or head_size is None:
+            raise RuntimeError("hybrid_decode_attention_absorbed: num_heads / head_size needed without kv_cache")
+        bs, h, d = hidden_cache.shape[2], num_heads, head_size
+    e = w_k.shape[1]
+    if query.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("hybrid_decode_attention_absorbed: fp16 or bf16 only")
+    bt = _i32(block_tables, "block_tables")
+    sl = _i32(seq_lens, "seq_lens")
+    ct = _i32(cache_type, "cache_type")
+    if hidden_rows is None:
+        hidden_rows = torch.nonzero(ct, as_tuple=False).flatten()
+    n_h = int(hidden_rows.shape[0])
+    max_tokens = bt.shape[1] * bs
+    # K/V-cached requests: the streaming path over the whole batch, hidden requests with length 0
+    if kv_cache is not None and n_h < b:
+        paged_decode_attention(query, kv_cache[0], kv_cache[1], bt, torch.where(ct != 0, torch.zeros_like(sl), sl),
+                               scale, out=out)
+    if n_h == 0:
+        return out
+    rows64 = hidden_rows.to(torch.int64)
+    rows32 = hidden_rows.to(torch.int32).contiguous()
+    hp = (h + 15) // 16 * 16
+    log2e = 1.4426950408889634
+    with torch.cuda.device(dev):
+        # fold: qa[h][i] = scale * log2(e) * W_k,h^T q[i][h]  (one batched GEMM over the heads,
+        # written in place: the kernels take the head-major layout)
+        q_h = (query.index_select(0, rows64).view(n_h, h, d).transpose(0, 1).float() * (scale * log2e)).to(query.dtype)
+        qa = _scratch(dev, "qa", hp * n_h * e, query.dtype).view(hp, n_h, e)
+        if hp != h:
+            qa[h:].zero_()
+        torch.bmm(q_h, w_k.view(h, d, e), out=qa[:h])
+        lens = sl.index_select(0, rows64).clamp(max=max_tokens).to(torch.int64)
+        tok_offset = torch.zeros(n_h + 1, dtype=torch.int64, device=dev)
+        torch.cumsum(lens, 0, out=tok_offset[1:])
+        scores = _scratch(dev, "scores", n_h * max_tokens * hp, torch.float32)
+        z = _scratch(dev, "z", hp * n_h * e, query.dtype).view(hp, n_h, e)
+        row_stride = hidden_cache.stride(2)
+        N.check(N.lib().aps_absorbed_hidden_attention(
+            N.ptr(z), N.ptr(scores), N.ptr(hidden_cache), N.ptr(qa), N.ptr(bt), N.ptr(sl), N.ptr(rows32),
+            N.ptr(tok_offset), n_h, bt.shape[1], bs, e, hp, row_stride, hidden_cache.numel() // row_stride,
+            N.dtype_enum(query), N.current_stream(dev)))
+        # unfold: out[i][h] = W_v,h z[i][h] + b_v
+        o = torch.bmm(z[:h], w_v.view(h, d, e).transpose(1, 2))                          # [h, n_h, d]
+        if b_v is not None:
+            o = o + b_v.view(h, 1, d)
+        out.index_copy_(0, rows64, o.transpose(0, 1).reshape(n_h, h * d).to(out.dtype))
+    return out
+
+
 def kv_reprojection(x: torch.Tensor, w_k: torch.Tensor, b_k: Optional[torch.Tensor],
                     w_v: torch.Tensor, b_v: Optional[torch.Tensor], head_size: int,
                     block_ids: Optional[torch.Tensor] = None, n_rows: Optional[int] = None,

@@ -19,8 +19,7 @@
  *  - every call enqueues on `stream` (a cudaStream_t passed as void*) of the
  *    CURRENT device and returns without synchronising;
  *  - nothing is allocated or freed for the caller and no pointer is retained
- *    after return (with APS_OVERLAP=1 in the environment the hybrid call creates a
- *    per-device side stream and two events on first use, kept until process exit);
+ *    after return;
  *  - the return value is an aps_status; no C++ exception crosses the boundary;
  *    aps_last_error() gives a human-readable message for the calling thread.
  */
@@ -307,6 +306,28 @@ int aps_expand_decode_metadata(const int32_t* block_tables, const int32_t* block
  * are cudaEvent_t handles owned by the caller; pass NULL, NULL to switch off.
  */
 int aps_set_profile_events(int which, void* start_event, void* stop_event);
+
+/*
+ * Hidden-path decode attention with the projections absorbed (no counterpart in the
+ * reference, which re-projects every cached hidden row, opt.py:111-124).  For a hidden
+ * request and head h, q.(W_k,h x_t + b_k) = (W_k,h^T q).x_t + const and
+ * sum_t p_t (W_v,h x_t + b_v) = W_v,h (sum_t p_t x_t) + b_v, so the cached hidden rows can
+ * be attended directly.  The caller folds `absorbed_query[h][i][:] = scale * log2(e) *
+ * W_k,h^T q[req_rows[i]][h]` ([heads_padded, n_req, hidden], model dtype, heads padded with
+ * zero rows to a multiple of 16: 16, 32, 48 or 80) with one batched GEMM; this call writes
+ * `scores` (scratch: [tok_offset[n_req], heads_padded] fp32, tok_offset = prefix sums of the
+ * hidden requests' clipped lengths) and `z[h][i][:] = sum_t softmax_t(scores)[t][h] x_t`
+ * ([heads_padded, n_req, hidden], model dtype); the caller unfolds out[h] = W_v,h z[h] + b_v
+ * with a second batched GEMM.  `block_tables` / `seq_lens` are the whole batch's; `req_rows`
+ * names the batch rows of the hidden requests.  fp16 / bf16, hidden_size % 512 == 0.
+ */
+int aps_absorbed_hidden_attention(void* z, float* scores, const void* hidden_cache,
+                                  const void* absorbed_query, const int32_t* block_tables,
+                                  const int32_t* seq_lens, const int32_t* req_rows,
+                                  const int64_t* tok_offset, int n_req, int max_blocks_per_seq,
+                                  int block_size, int hidden_size, int heads_padded,
+                                  int64_t hidden_row_stride, int64_t num_hidden_rows, int dtype,
+                                  void* stream);
 
 /*
  * Tensor-parallel exchange: the one collective of the path.  Replaces
