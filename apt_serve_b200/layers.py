@@ -16,7 +16,7 @@ import torch
 import torch.nn.functional as F
 
 from . import mixed_cache_ops, ops
-from .attention import Attention, hybrid_decode_attention
+from .attention import Attention, hybrid_decode_attention, hybrid_decode_attention_absorbed
 from .metadata import derive_private_block_tables
 
 
@@ -95,7 +95,8 @@ class OPTAttention(torch.nn.Module):
     cache -- into: Q projection, the new token's K/V projection and cache write
     for K/V requests, the new token's hidden row write for hidden requests, one
     hybrid decode attention call; a prefill batch with hidden-designated prompts
-    writes both kinds of cache rows with one launch.  ``fused=False`` runs the
+    writes both kinds of cache rows with one launch.  ``fused="absorbed"`` is the same with
+    the hidden requests attended through absorbed projections (fp16 / bf16).  ``fused=False`` runs the
     reference's op sequence literally on this package's kernels.
 
     Under tensor parallelism ``hidden_cache`` must be given (a
@@ -106,7 +107,7 @@ class OPTAttention(torch.nn.Module):
     def __init__(self, embed_dim: int, num_heads: int, qkv_weight: torch.Tensor,
                  qkv_bias: Optional[torch.Tensor], o_weight: torch.Tensor,
                  o_bias: Optional[torch.Tensor], tp_size: int = 1, group=None,
-                 fused: bool = True):
+                 fused=True):
         super().__init__()
         assert num_heads % tp_size == 0
         self.embed_dim = embed_dim
@@ -179,7 +180,12 @@ class OPTAttention(torch.nn.Module):
             k_new = kv[:, :hd].view(-1, self.num_heads, self.head_dim)
             v_new = kv[:, hd:].view(-1, self.num_heads, self.head_dim)
             ops.reshape_and_cache_flash(k_new, v_new, kv_cache[0], kv_cache[1], slots, "auto")
-        attn_output = hybrid_decode_attention(q, kv_cache, hidden_cache, w_k, b_k, w_v, b_v,
-                                              tables, m.seq_lens_tensor, ctype, self.scaling)
+        if self.fused == "absorbed" and q.dtype in (torch.float16, torch.bfloat16):
+            attn_output = hybrid_decode_attention_absorbed(
+                q, kv_cache, hidden_cache, w_k, b_k, w_v, b_v, tables, m.seq_lens_tensor, ctype,
+                self.scaling, hidden_rows=m.hidden_cache_use_input)
+        else:
+            attn_output = hybrid_decode_attention(q, kv_cache, hidden_cache, w_k, b_k, w_v, b_v,
+                                                  tables, m.seq_lens_tensor, ctype, self.scaling)
         output, _ = self.out_proj(attn_output)
         return output

@@ -82,3 +82,16 @@ def test_absorbed_ragged_sweep(seed):
     ref = oracle_out(w)
     out = absorbed(w.to("cuda"))
     assert_close(out, ref, f"absorbed sweep {seed}: lens={lens} hidden={hidden}")
+
+
+def test_opt_attention_with_absorbed_projections_matches_the_fused_layer():
+    from apt_serve_b200.layers import OPTAttention
+    w = small_workload(heads=4, head_dim=128, lens=(33, 70, 150, 9, 260), hidden=(True, False, True, False, True),
+                       device="cuda", with_shared_cache=True)
+    meta = A.FlashAttentionMetadata.from_decode(w.meta)
+    args = (w.shape.hidden, 4, w.qkv_weight, w.qkv_bias, w.o_weight, w.o_bias)
+    kv1, kv2 = w.kv_cache.clone(), w.kv_cache.clone()
+    y1 = OPTAttention(*args, fused=True)(w.hidden_states, kv1, None, meta)
+    y2 = OPTAttention(*args, fused="absorbed")(w.hidden_states, kv2, None, meta)
+    assert torch.equal(kv1, kv2)                          # the same cache writes
+    assert_close(y2, y1.float(), "OPTAttention absorbed vs fused", 3e-2, 3e-2)
