@@ -53,7 +53,7 @@ PROTOTYPES = {
                             [c_int64] * 4 + [c_int, c_void_p, c_void_p]),
     "aps_attention_status": (c_int, [c_void_p, c_void_p, c_void_p]),
     "aps_set_profile_events": (c_int, [c_int, c_void_p, c_void_p]),
-    "aps_absorbed_hidden_attention": (c_int, [c_void_p] * 8 + [c_int] * 5 + [c_int64, c_int64, c_int, c_void_p]),
+    "aps_absorbed_hidden_attention": (c_int, [c_void_p] * 9 + [c_int] * 5 + [c_int64, c_int64, c_int, c_void_p]),
     "aps_tp_unique_id": (c_int, [c_void_p]),
     "aps_tp_init": (c_int, [c_void_p, c_void_p, c_int, c_int]),
     "aps_tp_allreduce": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_void_p]),

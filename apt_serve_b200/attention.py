@@ -230,10 +230,11 @@ def hybrid_decode_attention_absorbed(query: torch.Tensor, kv_cache: Optional[tor
         tok_offset = torch.zeros(n_h + 1, dtype=torch.int64, device=dev)
         torch.cumsum(lens, 0, out=tok_offset[1:])
         scores = _scratch(dev, "scores", n_h * max_tokens * hp, torch.float32)
+        probs = _scratch(dev, "probs", n_h * max_tokens * hp, query.dtype)
         z = _scratch(dev, "z", hp * n_h * e, query.dtype).view(hp, n_h, e)
         row_stride = hidden_cache.stride(2)
         N.check(N.lib().aps_absorbed_hidden_attention(
-            N.ptr(z), N.ptr(scores), N.ptr(hidden_cache), N.ptr(qa), N.ptr(bt), N.ptr(sl), N.ptr(rows32),
+            N.ptr(z), N.ptr(scores), N.ptr(probs), N.ptr(hidden_cache), N.ptr(qa), N.ptr(bt), N.ptr(sl), N.ptr(rows32),
             N.ptr(tok_offset), n_h, bt.shape[1], bs, e, hp, row_stride, hidden_cache.numel() // row_stride,
             N.dtype_enum(query), N.current_stream(dev)))
         # unfold: out[i][h] = W_v,h z[i][h] + b_v

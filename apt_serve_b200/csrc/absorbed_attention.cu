@@ -9,15 +9,16 @@
 // With qa[r][h] = scale * log2(e) * W_k,h^T q[r][h] (an E-vector, folded by the caller with one
 // batched GEMM) the hidden rows are attended directly, K = V = X with a "head dimension" of
 // E, and the caller unfolds z[r][h] = sum_t p_t x_t with W_v,h in a second batched GEMM.
-// Two kernels, both streaming the hidden rows once (HBM-bound):
+// Three kernels, two of them streaming the hidden rows once:
 //   scores_kernel        S[t][h] = x_t . qa[r][h] for every cached token of every hidden
 //                        request: one CTA per 128-token tile (grid: tiles of the longest
 //                        possible request x requests; CTAs past a request's end return), mma.sync m16n8k16 over E in
 //                        64-element chunks staged by cp.async (3 stages);
-//   weighted_sum_kernel  z[r][h][e] = sum_t 2^(S[t][h] - max_t S) x_t[e] / sum: one CTA per
-//                        (request, 512-wide slice of E); softmax statistics from S in the
-//                        prologue, then 32-token sub-tiles: P in shared memory, X through
-//                        ldmatrix.trans, accumulators in registers.
+//   softmax_kernel       P[t][h] = softmax over the request's tokens of S[.][h], one CTA per
+//                        request (the scores are L2-resident);
+//   weighted_sum_kernel  z[r][h][e] = sum_t P[t][h] x_t[e]: one CTA per (request, 512-wide
+//                        slice of E), 32-token sub-tiles staged by cp.async (3 stages), P and X
+//                        both through ldmatrix.trans, accumulators in registers.
 // The legacy tensor path (mma.sync) is enough: per 16-byte of X loaded there are 6 resp. 12
 // MMAs, far below what keeps the loads from being the limit.
 #include <cuda_bf16.h>
@@ -36,7 +37,7 @@ constexpr int kScoreStages = 3;
 constexpr int kSumSlice = 512;      // columns of E per CTA of the weighted-sum kernel
 constexpr int kSumThreads = 256;    // 8 warps x 64 columns
 constexpr int kSumTokens = 32;      // tokens per sub-tile
-constexpr int kSumStages = 2;
+constexpr int kSumStages = 3;
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -81,6 +82,7 @@ struct AbsorbedArgs {
   const void* x;               // hidden cache, flat rows of x_row_stride elements
   const void* qa;              // [heads_padded][n_req][hidden] absorbed queries (model dtype)
   float* scores;               // [total tokens][heads_padded]
+  void* probs;                 // [total tokens][heads_padded] softmax weights (model dtype)
   void* z;                     // [heads_padded][n_req][hidden] (model dtype), weighted sums / softmax sum
   const int32_t* block_tables; // [batch][max_blocks] (all requests of the batch)
   const int32_t* seq_lens;     // [batch]
@@ -198,41 +200,110 @@ scores_kernel(const AbsorbedArgs a) {
   }
 }
 
-// ---- weighted sums ------------------------------------------------------------------
-// Shared memory: per stage an X sub-tile [32 tokens][512 columns] (rows of 1 KB, the 16-byte
-// piece j stored at (j & ~7) | ((j ^ row) & 7)) and the sub-tile's scores [32][HP] fp32; one
-// P tile [HP][32] in the model dtype with rows padded to 80 bytes; the statistics.
+// ---- softmax over a request's tokens ------------------------------------------------
+// One CTA per hidden request: P[t][h] = 2^(S[t][h] - max_t S[.][h]) / sum_t 2^(...), written in
+// the model dtype.  Thread (row group rg, column group cgp) walks rows rg, rg + R, ... with
+// 16-byte loads, four rows in flight, keeping a running (max, sum) for its four heads; the R row
+// groups are merged through shared memory; a second walk writes P.
 template <typename T> struct Pack2;
 template <> struct Pack2<__half> {
-  static __device__ __forceinline__ __half one(float v) { return __float2half_rn(v); }
+  static __device__ __forceinline__ uint32_t two(float lo, float hi) {
+    const __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
 };
 template <> struct Pack2<__nv_bfloat16> {
-  static __device__ __forceinline__ __nv_bfloat16 one(float v) { return __float2bfloat16_rn(v); }
+  static __device__ __forceinline__ uint32_t two(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
 };
 
+template <typename T, int HP>
+__global__ void __launch_bounds__(kSumThreads)
+softmax_kernel(const AbsorbedArgs a) {
+  constexpr int G = HP / 4, R = kSumThreads / G;
+  __shared__ float s_red[R * HP * 2];
+  __shared__ float s_max[HP], s_inv[HP];
+  const int ri = blockIdx.x;
+  const int req = a.req_rows[ri];
+  const int seq = min(a.seq_lens[req], a.max_blocks * a.block_size);
+  const float* sc = a.scores + a.tok_offset[ri] * HP;
+  T* pr = static_cast<T*>(a.probs) + a.tok_offset[ri] * HP;
+  const int cgp = threadIdx.x % G, rg = threadIdx.x / G;
+  const float4* src = reinterpret_cast<const float4*>(sc) + cgp;
+  float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY}, l4[4] = {0.f, 0.f, 0.f, 0.f};
+  if (rg < R) {
+    for (int t = rg; t < seq; t += 4 * R) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        v[u] = t + u * R < seq ? src[(int64_t)(t + u * R) * G]
+                               : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float e4[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const float mn = fmaxf(m4[c], e4[c]);
+          if (mn > -INFINITY) l4[c] = l4[c] * exp2f(m4[c] - mn) + exp2f(e4[c] - mn);
+          m4[c] = mn;
+        }
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      s_red[(rg * HP + cgp * 4 + c) * 2] = m4[c];
+      s_red[(rg * HP + cgp * 4 + c) * 2 + 1] = l4[c];
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < HP) {
+    float m = -INFINITY, l = 0.f;
+    for (int r = 0; r < R; ++r) m = fmaxf(m, s_red[(r * HP + threadIdx.x) * 2]);
+    for (int r = 0; r < R; ++r) {
+      const float mr = s_red[(r * HP + threadIdx.x) * 2];
+      if (mr > -INFINITY) l += s_red[(r * HP + threadIdx.x) * 2 + 1] * exp2f(mr - m);
+    }
+    s_max[threadIdx.x] = m;
+    s_inv[threadIdx.x] = l > 0.f ? 1.f / l : 0.f;
+  }
+  __syncthreads();
+  if (rg < R) {
+    const float mx[4] = {s_max[cgp * 4], s_max[cgp * 4 + 1], s_max[cgp * 4 + 2], s_max[cgp * 4 + 3]};
+    const float iv[4] = {s_inv[cgp * 4], s_inv[cgp * 4 + 1], s_inv[cgp * 4 + 2], s_inv[cgp * 4 + 3]};
+    for (int t = rg; t < seq; t += R) {
+      const float4 v = src[(int64_t)t * G];
+      uint2 o;
+      o.x = Pack2<T>::two(exp2f(v.x - mx[0]) * iv[0], exp2f(v.y - mx[1]) * iv[1]);
+      o.y = Pack2<T>::two(exp2f(v.z - mx[2]) * iv[2], exp2f(v.w - mx[3]) * iv[3]);
+      *reinterpret_cast<uint2*>(pr + (int64_t)t * HP + cgp * 4) = o;
+    }
+  }
+}
+
+// ---- weighted sums ------------------------------------------------------------------
+// z[h][e] = sum_t P[t][h] x_t[e] for one request and one 512-wide slice of E.  Shared memory
+// per stage: an X sub-tile [32 tokens][512 columns] (rows of 1 KB, the 16-byte piece j stored
+// at (j & ~7) | ((j ^ row) & 7)) and the sub-tile's P rows [32][HP] (rows padded by 16 bytes).
+// Both operands are read with ldmatrix.trans: the tokens are the rows of both tiles and the
+// contraction runs over them.
 template <typename T, int HP>
 __global__ void __launch_bounds__(kSumThreads)
 weighted_sum_kernel(const AbsorbedArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int kXBytes = kSumTokens * kSumSlice * 2;          // 32 KB
-  constexpr int kSBytes = kSumTokens * HP * 4;
-  constexpr int kStage = kXBytes + kSBytes;
-  constexpr int kPRow = 80;                                    // bytes per P row (32 tokens + pad)
-  uint8_t* p_tile = smem + kSumStages * kStage;
-  float* s_max = reinterpret_cast<float*>(p_tile + HP * kPRow);
-  float* s_sum = s_max + HP;
-  float* s_red = s_sum + HP;                                   // [row groups][HP][2] scratch of the statistics
-
+  constexpr int kPRow = HP * 2 + 16;                           // bytes per P row in shared memory
+  constexpr int kStage = kXBytes + kSumTokens * kPRow;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int ri = blockIdx.y, slice = blockIdx.x;
   const int req = a.req_rows[ri];
   const int seq = min(a.seq_lens[req], a.max_blocks * a.block_size);
   const int32_t* bt = a.block_tables + (int64_t)req * a.max_blocks;
   const T* x = static_cast<const T*>(a.x) + (int64_t)slice * kSumSlice;
-  const float* sc = a.scores + a.tok_offset[ri] * HP;
+  const T* pr = static_cast<const T*>(a.probs) + a.tok_offset[ri] * HP;
   const int n_sub = (seq + kSumTokens - 1) / kSumTokens;
 
-  // ---- the first stages go out before the statistics are formed ----
   const uint32_t base = smem_addr(smem);
   auto issue = [&](int sub, int stage) {
     const uint32_t s = base + stage * kStage;
@@ -252,11 +323,12 @@ weighted_sum_kernel(const AbsorbedArgs a) {
         cp_async16(s + row * 1024 + (((j & ~7) | ((j ^ row) & 7)) << 4), x + (ok ? xr : 0) * a.x_row_stride + j * 8, ok);
       }
     }
-    // scores: 32 rows x HP floats, contiguous in global memory
-    constexpr int kSPieces = kSumTokens * HP / 4;
-    for (int pce = threadIdx.x; pce < kSPieces; pce += kSumThreads) {
-      const int tok = sub * kSumTokens + pce / (HP / 4);
-      cp_async16(s + kXBytes + pce * 16, sc + (int64_t)sub * kSumTokens * HP + pce * 4, tok < seq);
+    // P: 32 rows x HP / 8 pieces (rows past the end are zero-filled: they weigh nothing)
+    constexpr int kPPieces = kSumTokens * (HP / 8);
+    for (int pce = threadIdx.x; pce < kPPieces; pce += kSumThreads) {
+      const int row = pce / (HP / 8), jj = pce % (HP / 8);
+      const int tok = sub * kSumTokens + row;
+      cp_async16(s + kXBytes + row * kPRow + jj * 16, pr + (int64_t)(tok < seq ? tok : 0) * HP + jj * 8, tok < seq);
     }
   };
 #pragma unroll
@@ -264,53 +336,6 @@ weighted_sum_kernel(const AbsorbedArgs a) {
     if (s < n_sub) issue(s, s);
     cp_async_commit();
   }
-  // ---- statistics: max and sum of 2^(s - max) over the request's tokens, per head ----
-  // Thread (row group rg, column group cgp) walks rows rg, rg + R, ... of the request's scores
-  // with 16-byte loads, four rows in flight, keeping a running (max, sum) for its four heads;
-  // the R row groups are merged through shared memory.
-  {
-    constexpr int G = HP / 4, R = kSumThreads / G;
-    const int cgp = threadIdx.x % G, rg = threadIdx.x / G;
-    float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY}, l4[4] = {0.f, 0.f, 0.f, 0.f};
-    if (rg < R) {
-      const float4* src = reinterpret_cast<const float4*>(sc) + cgp;
-      for (int t = rg; t < seq; t += 4 * R) {
-        float4 v[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u)
-          v[u] = t + u * R < seq ? src[(int64_t)(t + u * R) * G] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const float e4[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const float mn = fmaxf(m4[c], e4[c]);
-            if (mn > -INFINITY) l4[c] = l4[c] * exp2f(m4[c] - mn) + exp2f(e4[c] - mn);
-            m4[c] = mn;
-          }
-        }
-      }
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        s_red[(rg * HP + cgp * 4 + c) * 2] = m4[c];
-        s_red[(rg * HP + cgp * 4 + c) * 2 + 1] = l4[c];
-      }
-    }
-    __syncthreads();
-    if (threadIdx.x < HP) {
-      float m = -INFINITY, l = 0.f;
-      for (int r = 0; r < R; ++r) m = fmaxf(m, s_red[(r * HP + threadIdx.x) * 2]);
-      for (int r = 0; r < R; ++r) {
-        const float mr = s_red[(r * HP + threadIdx.x) * 2];
-        if (mr > -INFINITY) l += s_red[(r * HP + threadIdx.x) * 2 + 1] * exp2f(mr - m);
-      }
-      s_max[threadIdx.x] = m;
-      s_sum[threadIdx.x] = l;
-    }
-    __syncthreads();
-  }
-
-  // ---- main loop ----
   float acc[HP / 16][8][4];
 #pragma unroll
   for (int m = 0; m < HP / 16; ++m)
@@ -318,30 +343,18 @@ weighted_sum_kernel(const AbsorbedArgs a) {
     for (int n = 0; n < 8; ++n)
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[m][n][e] = 0.f;
-  // A (P: 16 heads x 16 tokens per matrix group): (heads 0-7, t 0-7), (heads 8-15, t 0-7),
-  // (heads 0-7, t 8-15), (heads 8-15, t 8-15); B through ldmatrix.trans from X[token][column]:
-  // (t 0-7, cols 0-7), (t 8-15, cols 0-7), (t 0-7, cols 8-15), (t 8-15, cols 8-15)
-  const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_piece = lane >> 4;
+  // A = P^T (16 heads x 16 tokens) through ldmatrix.trans from P[token][head]: matrices
+  // (t 0-7, heads 0-7), (t 0-7, heads 8-15), (t 8-15, heads 0-7), (t 8-15, heads 8-15);
+  // B through ldmatrix.trans from X[token][column]: (t 0-7, cols 0-7), (t 8-15, cols 0-7),
+  // (t 0-7, cols 8-15), (t 8-15, cols 8-15)
+  const int a_row = (lane & 7) + ((lane >> 4) & 1) * 8, a_piece = (lane >> 3) & 1;
   const int b_row = (lane & 7) + ((lane >> 3) & 1) * 8, b_piece = lane >> 4;
   for (int sub = 0; sub < n_sub; ++sub) {
     cp_async_wait<kSumStages - 2>();
-    __syncthreads();   // the stage has landed; everyone is done with the P tile of the last sub-tile
+    __syncthreads();   // the stage has landed; everyone is done with the stage refilled next
     if (sub + kSumStages - 1 < n_sub) issue(sub + kSumStages - 1, (sub + kSumStages - 1) % kSumStages);
     cp_async_commit();
     const uint32_t s = base + (sub % kSumStages) * kStage;
-    // P[h][t] = 2^(S[t][h] - max[h]) (0 past the end: the scores of such rows are zero-filled,
-    // so they are masked here)
-    {
-      const float* s_tile = reinterpret_cast<const float*>(smem + (sub % kSumStages) * kStage + kXBytes);
-      for (int idx = threadIdx.x; idx < HP * kSumTokens; idx += kSumThreads) {
-        const int t = idx / HP, h = idx - t * HP;
-        const bool live = sub * kSumTokens + t < seq;
-        const float pv = live ? exp2f(s_tile[t * HP + h] - s_max[h]) : 0.f;
-        *reinterpret_cast<T*>(p_tile + h * kPRow + t * 2) = Pack2<T>::one(pv);
-      }
-    }
-    __syncthreads();
-    const uint32_t p_base = smem_addr(p_tile);
 #pragma unroll
     for (int ks = 0; ks < kSumTokens / 16; ++ks) {
       uint32_t bfr[4][4];
@@ -354,7 +367,7 @@ weighted_sum_kernel(const AbsorbedArgs a) {
 #pragma unroll
       for (int m = 0; m < HP / 16; ++m) {
         uint32_t af[4];
-        ldmatrix_x4(p_base + (m * 16 + a_row) * kPRow + ((ks * 2 + a_piece) << 4), af);
+        ldmatrix_x4_trans(s + kXBytes + (ks * 16 + a_row) * kPRow + ((m * 2 + a_piece) << 4), af);
 #pragma unroll
         for (int np = 0; np < 4; ++np) {
           mma16816<T>(acc[m][np * 2], af, bfr[np][0], bfr[np][1]);
@@ -364,7 +377,7 @@ weighted_sum_kernel(const AbsorbedArgs a) {
     }
   }
   cp_async_wait<0>();
-  // ---- z = acc / sum ----
+  // C fragment: heads g and g + 8 of every 16-head tile, columns 2c, 2c + 1 of every 8-column tile
   const int g = lane >> 2, cq = lane & 3;
   T* z = static_cast<T*>(a.z) + (int64_t)ri * a.hidden + (int64_t)slice * kSumSlice + warp * 64;
 #pragma unroll
@@ -372,13 +385,10 @@ weighted_sum_kernel(const AbsorbedArgs a) {
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
       const int h = m * 16 + g + half * 8;
-      const float inv = seq > 0 ? 1.f / s_sum[h] : 0.f;
 #pragma unroll
-      for (int n = 0; n < 8; ++n) {
-        T* dst = z + (int64_t)h * a.n_req * a.hidden + n * 8 + cq * 2;
-        dst[0] = Pack2<T>::one(acc[m][n][half * 2] * inv);
-        dst[1] = Pack2<T>::one(acc[m][n][half * 2 + 1] * inv);
-      }
+      for (int n = 0; n < 8; ++n)
+        *reinterpret_cast<uint32_t*>(z + (int64_t)h * a.n_req * a.hidden + n * 8 + cq * 2) =
+            Pack2<T>::two(acc[m][n][half * 2], acc[m][n][half * 2 + 1]);
     }
 }
 
@@ -393,8 +403,12 @@ int launch_absorbed(const AbsorbedArgs& a, cudaStream_t stream) {
     int st = launch_status("scores_kernel");
     if (st != APS_OK) return st;
   }
-  constexpr size_t smem2 = (size_t)kSumStages * (kSumTokens * kSumSlice * 2 + kSumTokens * HP * 4) +
-                           HP * 80 + (2 + 2 * (kSumThreads / (HP / 4))) * HP * sizeof(float);
+  softmax_kernel<T, HP><<<a.n_req, kSumThreads, 0, stream>>>(a);
+  {
+    int st = launch_status("softmax_kernel");
+    if (st != APS_OK) return st;
+  }
+  constexpr size_t smem2 = (size_t)kSumStages * (kSumTokens * kSumSlice * 2 + kSumTokens * (HP * 2 + 16));
   auto k2 = weighted_sum_kernel<T, HP>;
   APS_CUDA(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2));
   k2<<<dim3(a.hidden / kSumSlice, a.n_req), kSumThreads, smem2, stream>>>(a);
@@ -415,7 +429,7 @@ int launch_absorbed_hp(const AbsorbedArgs& a, cudaStream_t stream) {
 }  // namespace
 }  // namespace aps
 
-extern "C" int aps_absorbed_hidden_attention(void* z, float* scores, const void* hidden_cache,
+extern "C" int aps_absorbed_hidden_attention(void* z, float* scores, void* probs, const void* hidden_cache,
                                              const void* absorbed_query, const int32_t* block_tables,
                                              const int32_t* seq_lens, const int32_t* req_rows,
                                              const int64_t* tok_offset,
@@ -427,7 +441,7 @@ extern "C" int aps_absorbed_hidden_attention(void* z, float* scores, const void*
   const char* op = "absorbed_hidden_attention";
   APS_REQUIRE(n_req >= 0 && n_req <= 65535, APS_ERR_SHAPE, "%s: 0..65535 hidden requests", op);
   if (n_req == 0) return APS_OK;
-  APS_REQUIRE(z && scores && hidden_cache && absorbed_query && block_tables && seq_lens && req_rows &&
+  APS_REQUIRE(z && scores && probs && hidden_cache && absorbed_query && block_tables && seq_lens && req_rows &&
                   tok_offset,
               APS_ERR_NULL_POINTER, "%s: null pointer", op);
   APS_REQUIRE(dtype == APS_F16 || dtype == APS_BF16, APS_ERR_DTYPE, "%s: fp16 or bf16 only", op);
@@ -436,9 +450,9 @@ extern "C" int aps_absorbed_hidden_attention(void* z, float* scores, const void*
   APS_REQUIRE(block_size > 0 && block_size % 16 == 0 && max_blocks_per_seq > 0, APS_ERR_UNSUPPORTED,
               "%s: block size %d", op, block_size);
   APS_REQUIRE(hidden_row_stride >= hidden_size && hidden_row_stride % 8 == 0 && aligned_to(hidden_cache, 16) &&
-                  aligned_to(absorbed_query, 16) && aligned_to(z, 16) && aligned_to(scores, 16),
+                  aligned_to(absorbed_query, 16) && aligned_to(z, 16) && aligned_to(scores, 16) && aligned_to(probs, 16),
               APS_ERR_MISALIGNED, "%s: rows must be 16-byte aligned", op);
-  AbsorbedArgs a{hidden_cache, absorbed_query, scores, z, block_tables, seq_lens, req_rows, tok_offset,
+  AbsorbedArgs a{hidden_cache, absorbed_query, scores, probs, z, block_tables, seq_lens, req_rows, tok_offset,
                  n_req, max_blocks_per_seq, block_size, hidden_size, heads_padded,
                  hidden_row_stride, num_hidden_rows};
   cudaStream_t cs = (cudaStream_t)stream;

@@ -316,12 +316,13 @@ int aps_set_profile_events(int which, void* start_event, void* stop_event);
  * W_k,h^T q[req_rows[i]][h]` ([heads_padded, n_req, hidden], model dtype, heads padded with
  * zero rows to a multiple of 16: 16, 32, 48 or 80) with one batched GEMM; this call writes
  * `scores` (scratch: [tok_offset[n_req], heads_padded] fp32, tok_offset = prefix sums of the
- * hidden requests' clipped lengths) and `z[h][i][:] = sum_t softmax_t(scores)[t][h] x_t`
+ * hidden requests' clipped lengths), `probs` (scratch of the same shape in the model dtype:
+ * the softmax of the scores over each request's tokens) and `z[h][i][:] = sum_t softmax_t(scores)[t][h] x_t`
  * ([heads_padded, n_req, hidden], model dtype); the caller unfolds out[h] = W_v,h z[h] + b_v
  * with a second batched GEMM.  `block_tables` / `seq_lens` are the whole batch's; `req_rows`
  * names the batch rows of the hidden requests.  fp16 / bf16, hidden_size % 512 == 0.
  */
-int aps_absorbed_hidden_attention(void* z, float* scores, const void* hidden_cache,
+int aps_absorbed_hidden_attention(void* z, float* scores, void* probs, const void* hidden_cache,
                                   const void* absorbed_query, const int32_t* block_tables,
                                   const int32_t* seq_lens, const int32_t* req_rows,
                                   const int64_t* tok_offset, int n_req, int max_blocks_per_seq,
