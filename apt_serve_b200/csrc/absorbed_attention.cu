@@ -289,7 +289,7 @@ softmax_kernel(const AbsorbedArgs a) {
 // Both operands are read with ldmatrix.trans: the tokens are the rows of both tiles and the
 // contraction runs over them.
 template <typename T, int HP>
-__global__ void __launch_bounds__(kSumThreads)
+__global__ void __launch_bounds__(kSumThreads, HP <= 48 ? 2 : 1)
 weighted_sum_kernel(const AbsorbedArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int kXBytes = kSumTokens * kSumSlice * 2;          // 32 KB
@@ -411,6 +411,8 @@ int launch_absorbed(const AbsorbedArgs& a, cudaStream_t stream) {
   constexpr size_t smem2 = (size_t)kSumStages * (kSumTokens * kSumSlice * 2 + kSumTokens * (HP * 2 + 16));
   auto k2 = weighted_sum_kernel<T, HP>;
   APS_CUDA(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2));
+  // two CTAs per SM need the largest shared-memory carve-out
+  APS_CUDA(cudaFuncSetAttribute(k2, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
   k2<<<dim3(a.hidden / kSumSlice, a.n_req), kSumThreads, smem2, stream>>>(a);
   return launch_status("weighted_sum_kernel");
 }
