@@ -544,6 +544,8 @@ def run_reference(args):
     rank, _, world = dist_env()
     if rank != 0:
         return
+    # all host cores, also under torchrun (which exports OMP_NUM_THREADS=1 to its ranks)
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
     from apt_serve_b200.workloads import CONFIG_SHAPES, draw_decode_batch, make_decode_workload
     cfg = args.config
     shape = CONFIG_SHAPES[cfg]
