@@ -271,6 +271,8 @@ class LayerStep:
         """The same step with the hidden requests attended through absorbed projections
         (attention.hybrid_decode_attention_absorbed) instead of the re-projecting kernel."""
         w, m = self.w, self.w.meta
+        if w.prefill is not None:
+            self.prefill_writes()
         self.cache_writes(w.hidden_states, w.new_key, w.new_value, self.kv_new_slots)
         out = self.A.hybrid_decode_attention_absorbed(
             w.query, w.kv_cache, w.hidden_cache, self.wk, self.bk, self.wv, self.bv, m.private_block_tables,
