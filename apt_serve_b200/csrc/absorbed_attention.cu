@@ -12,15 +12,17 @@
 // Three kernels, two of them streaming the hidden rows once:
 //   scores_kernel        S[t][h] = x_t . qa[r][h] for every cached token of every hidden
 //                        request: one CTA per 128-token tile (grid: tiles of the longest
-//                        possible request x requests; CTAs past a request's end return), mma.sync m16n8k16 over E in
-//                        64-element chunks staged by cp.async (3 stages);
+//                        possible request x requests; CTAs past a request's end return),
+//                        mma.sync m16n8k16 over E in 64-element chunks staged by cp.async
+//                        (3 stages);
 //   softmax_kernel       P[t][h] = softmax over the request's tokens of S[.][h], one CTA per
 //                        request (the scores are L2-resident);
 //   weighted_sum_kernel  z[r][h][e] = sum_t P[t][h] x_t[e]: one CTA per (request, 512-wide
 //                        slice of E), 32-token sub-tiles staged by cp.async (3 stages), P and X
 //                        both through ldmatrix.trans, accumulators in registers.
-// The legacy tensor path (mma.sync) is enough: per 16-byte of X loaded there are 6 resp. 12
-// MMAs, far below what keeps the loads from being the limit.
+// The warp-level mma.sync is used on purpose: both products have a tiny N (the padded head
+// count) and a few MMAs per 16 bytes of X loaded, so the kernels are bound by streaming X,
+// not by the tensor pipe.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -83,7 +85,7 @@ struct AbsorbedArgs {
   const void* qa;              // [heads_padded][n_req][hidden] absorbed queries (model dtype)
   float* scores;               // [total tokens][heads_padded]
   void* probs;                 // [total tokens][heads_padded] softmax weights (model dtype)
-  void* z;                     // [heads_padded][n_req][hidden] (model dtype), weighted sums / softmax sum
+  void* z;                     // [heads_padded][n_req][hidden] (model dtype): the softmax-weighted sums of the hidden rows
   const int32_t* block_tables; // [batch][max_blocks] (all requests of the batch)
   const int32_t* seq_lens;     // [batch]
   const int32_t* req_rows;     // [n_req] batch row of every hidden request
