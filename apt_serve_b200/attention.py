@@ -215,7 +215,10 @@ def hybrid_decode_attention_absorbed(query: torch.Tensor, kv_cache: Optional[tor
     if n_h == 0:
         return out
     rows64 = hidden_rows.to(torch.int64)
-    rows32 = hidden_rows.to(torch.int32).contiguous()
+    # longest requests first: the kernels' CTAs are dispatched in request order and a CTA's
+    # run time grows with its request's length
+    rows64 = rows64[torch.argsort(sl.index_select(0, rows64), descending=True)]
+    rows32 = rows64.to(torch.int32)
     hp = (h + 15) // 16 * 16
     log2e = 1.4426950408889634
     with torch.cuda.device(dev):
