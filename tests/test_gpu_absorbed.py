@@ -95,3 +95,20 @@ def test_opt_attention_with_absorbed_projections_matches_the_fused_layer():
     y2 = OPTAttention(*args, fused="absorbed")(w.hidden_states, kv2, None, meta)
     assert torch.equal(kv1, kv2)                          # the same cache writes
     assert_close(y2, y1.float(), "OPTAttention absorbed vs fused", 3e-2, 3e-2)
+
+
+def test_absorbed_opt66b_bf16_tensor_parallel_slice():
+    """Config-4 shapes at tp = 8: 9 heads per rank (padded to 16), E = 9216, dedicated hidden
+    tensor; the rank's output equals its slice of the full-width oracle result."""
+    from apt_serve_b200.workloads import OPT_66B, draw_decode_batch, make_decode_workload
+    lens, hid = draw_decode_batch(4, batch=6)
+    lens = [min(s, 400) for s in lens]
+    hid[0], hid[1] = True, False
+    full = make_decode_workload(OPT_66B, lens, hid, seed=1004, device="cuda")
+    ref_full = oracle_out(full.cpu())
+    rank = 5
+    w = make_decode_workload(OPT_66B, lens, hid, seed=1004, device="cuda", tp_rank=rank, tp_size=8)
+    w.hidden_cache.view(-1, 9216).copy_(full.hidden_cache.view(-1, 9216))   # replicated hidden rows
+    out = absorbed(w)
+    sl = slice(rank * 9 * 128, (rank + 1) * 9 * 128)
+    assert_close(out, ref_full[:, sl], "absorbed, tp rank 5")
