@@ -51,7 +51,12 @@ PROTOTYPES = {
                                     [c_float, c_void_p, c_size_t, c_int, c_void_p]),
     "aps_kv_reprojection": (c_int, [c_void_p] * 3 + [c_int64] + [c_void_p] * 4 + [c_int] * 3 +
                             [c_int64] * 4 + [c_int, c_void_p, c_void_p]),
+    "aps_decode_layer_step": (c_int, [c_void_p] * 15 + [c_int] * 6 + [c_int64] * 9 +
+                              [c_float, c_void_p, c_size_t, c_int, c_void_p]),
     "aps_attention_status": (c_int, [c_void_p, c_void_p, c_void_p]),
+    "aps_cache_ops_status": (c_int, [c_void_p, c_void_p]),
+    "aps_selftest_bounded_wait": (c_int, [c_void_p, c_size_t, ctypes.c_longlong, c_void_p] + [c_int] * 5 +
+                                  [c_int64, c_int, c_void_p]),
     "aps_set_profile_events": (c_int, [c_int, c_void_p, c_void_p]),
     "aps_absorbed_hidden_attention": (c_int, [c_void_p] * 9 + [c_int] * 5 + [c_int64, c_int64, c_int, c_void_p]),
     "aps_tp_unique_id": (c_int, [c_void_p]),

@@ -56,6 +56,26 @@ def attention_status(workspace: torch.Tensor) -> int:
     return host.value
 
 
+def raise_on_device_status(workspace: Optional[torch.Tensor] = None,
+                           device: Optional[torch.device] = None) -> None:
+    """Raise ``RuntimeError`` if the last attention call on ``workspace`` (default: the
+    per-device workspace of ``device``) left a non-zero status word: 1..7 = a bounded wait
+    of the re-projection kernel ran out and the call's output is NaN, 8 = K/V-cached
+    requests in a batch that was given no K/V cache.  Synchronises the current stream, so
+    call it where a synchronisation is cheap (once per engine step, beside the sampler's
+    device-to-host copy), not per layer."""
+    if workspace is None:
+        workspace = _workspaces.get(torch.device(device) if device is not None
+                                    else torch.device("cuda", torch.cuda.current_device()))
+        if workspace is None:
+            return
+    code = attention_status(workspace)
+    if code != 0:
+        what = ("a bounded device-side wait ran out; the output was filled with NaN" if code < 8 else
+                "the batch holds K/V-cached requests but no K/V cache was passed; their rows are zero")
+        raise RuntimeError(f"aptserve_b200: attention status {code}: {what}")
+
+
 def _i32(t: torch.Tensor, name: str) -> torch.Tensor:
     if t.dtype != torch.int32:
         raise RuntimeError(f"{name} must be int32 (got {t.dtype})")
@@ -152,6 +172,76 @@ def hybrid_decode_attention(query: torch.Tensor, kv_cache: Optional[torch.Tensor
             w_k.stride(0), float(scale), N.ptr(workspace), workspace.numel(),
             N.dtype_enum(query), N.current_stream(dev)))
     return out
+
+
+def decode_layer_step(query: torch.Tensor, hidden_states: Optional[torch.Tensor],
+                      new_key: Optional[torch.Tensor], new_value: Optional[torch.Tensor],
+                      kv_cache: Optional[torch.Tensor], hidden_cache: torch.Tensor,
+                      w_k: torch.Tensor, b_k: Optional[torch.Tensor], w_v: torch.Tensor,
+                      b_v: Optional[torch.Tensor], block_tables: torch.Tensor,
+                      seq_lens: torch.Tensor, cache_type: torch.Tensor, scale: float,
+                      num_heads: Optional[int] = None, head_size: Optional[int] = None,
+                      out: Optional[torch.Tensor] = None,
+                      workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One decode layer-step in one native call (``aps_decode_layer_step``): the new token's
+    cache writes -- ``hidden_states[r]`` into the hidden cache for hidden-cached requests
+    (aptserve_opt.py:108-109), ``new_key[r]`` / ``new_value[r]`` into the K/V planes for
+    K/V-cached requests (aptserve_flash_attn.py:338-345, 363-373) -- addressed from the
+    private block tables, then ``hybrid_decode_attention`` over the batch.  ``new_key`` /
+    ``new_value``: ``[B, H*D]`` (or ``[B, H, D]``) with any row stride; rows of requests of
+    the other cache type are ignored.  ``None`` skips that kind of write."""
+    dev = N.require_cuda(query, hidden_states, new_key, new_value, kv_cache, hidden_cache, w_k, b_k,
+                         w_v, b_v, block_tables, seq_lens, cache_type)
+    b = query.shape[0]
+    if out is None:
+        out = torch.empty_like(query)
+    if b == 0:
+        return out
+    if kv_cache is not None:
+        _, _, bs, h, d = kv_cache.shape
+        kc, vc, block_stride = kv_cache[0], kv_cache[1], kv_cache.stride(1)
+    else:
+        if num_heads is None or head_size is None:
+            raise RuntimeError("decode_layer_step: num_heads / head_size needed without kv_cache")
+        bs, h, d = hidden_cache.shape[2], num_heads, head_size
+        kc = vc = None
+        block_stride = bs * h * d
+        new_key = new_value = None
+    e = w_k.shape[1]
+    if w_k.shape != w_v.shape or w_k.stride(0) != w_v.stride(0) or w_k.stride(1) != 1:
+        raise RuntimeError("decode_layer_step: W_k / W_v must be row-major with equal strides")
+    if w_k.shape[0] != h * d:
+        raise RuntimeError("decode_layer_step: W_k has %d rows, expected H*D = %d" % (w_k.shape[0], h * d))
+    if (new_key is None) != (new_value is None):
+        raise RuntimeError("decode_layer_step: new_key and new_value go together")
+    for name, t in (("hidden_states", hidden_states), ("new_key", new_key), ("new_value", new_value)):
+        if t is not None and (t.shape[0] != b or t.stride(-1) != 1):
+            raise RuntimeError(f"decode_layer_step: {name} must hold one contiguous row per request")
+    row_stride = hidden_cache.stride(2)
+    n_rows = hidden_cache.numel() // row_stride
+    bt = _i32(block_tables, "block_tables")
+    sl = _i32(seq_lens, "seq_lens")
+    ct = _i32(cache_type, "cache_type")
+    if workspace is None:
+        workspace = attention_workspace(dev, b, bt.shape[1], bs, h, d)
+    with torch.cuda.device(dev):
+        N.check(N.lib().aps_decode_layer_step(
+            N.ptr(out), N.ptr(query), N.ptr(hidden_states), N.ptr(new_key), N.ptr(new_value),
+            N.ptr(kc), N.ptr(vc), N.ptr(hidden_cache), N.ptr(w_k), N.ptr(b_k), N.ptr(w_v), N.ptr(b_v),
+            N.ptr(bt), N.ptr(sl), N.ptr(ct), b, bt.shape[1], h, d, e, bs, query.stride(0), out.stride(0),
+            0 if hidden_states is None else hidden_states.stride(0),
+            0 if new_key is None else new_key.stride(0), 0 if new_value is None else new_value.stride(0),
+            block_stride, row_stride, n_rows, w_k.stride(0), float(scale), N.ptr(workspace),
+            workspace.numel(), N.dtype_enum(query), N.current_stream(dev)))
+    return out
+
+
+def absorbed_supported(num_heads: int, hidden_size: int, dtype: torch.dtype) -> bool:
+    """Whether ``hybrid_decode_attention_absorbed`` takes this shape: fp16 / bf16, the head
+    count padded to a multiple of 16 must be 16, 32, 48 or 80, hidden size a multiple of 512."""
+    hp = (num_heads + 15) // 16 * 16
+    return (dtype in (torch.float16, torch.bfloat16) and hp in (16, 32, 48, 80)
+            and hidden_size % 512 == 0)
 
 
 _absorbed_scratch: Dict[torch.device, Dict[str, torch.Tensor]] = {}
@@ -288,7 +378,9 @@ class FlashAttentionBackend:
 
     @staticmethod
     def get_supported_head_sizes() -> List[int]:
-        return [32, 64, 96, 128, 160, 192, 224, 256]
+        # what the decode kernels take (the reference's flash-attn list, aptserve_flash_attn.py:19,
+        # also names 96, 160, 192, 224; OPT uses 64 and 128)
+        return [32, 64, 128, 256]
 
     @staticmethod
     def get_name() -> str:
@@ -503,13 +595,13 @@ class FlashAttentionImpl:
                 ops.reshape_and_cache_flash(key, value, key_cache, value_cache, m.slot_mapping,
                                             self.kv_cache_dtype)
             elif n_prefill != 0:
-                # K/V are cached for the K/V-designated prompt tokens only.  Masking the
-                # other tokens' slots to -1 writes exactly the rows the reference's
-                # index-select copy writes, without materialising key[kv_cache_use_tot].
-                slots = torch.full_like(m.slot_mapping, -1)
-                slots[m.kv_cache_use_tot] = m.slot_mapping[m.kv_cache_use_tot]
-                ops.reshape_and_cache_flash(key, value, key_cache, value_cache, slots,
-                                            self.kv_cache_dtype)
+                # K/V are cached for the K/V-designated prompt tokens only: the rows listed in
+                # kv_cache_use_tot go straight from the packed tensors to their slots, which
+                # writes exactly what the reference's index-select copy
+                # (reshape_and_cache_flash(key[kv_cache_use_tot], ...)) writes, without
+                # materialising the gathered tensors
+                ops.prefill_cache_write(key, value, None, kv_cache, None, m.slot_mapping,
+                                        m.kv_cache_use_tot, None)
             else:
                 shared_k, shared_v = shared_cache[0], shared_cache[1]
                 if m.num_tot_tokens != len(m.slot_mapping_shared):

@@ -23,11 +23,22 @@ enum PlanWord {
   kPlanNumHidTiles = 1,   // chunks (M tiles) of hidden-cached requests
   kPlanKvCounter = 2,     // dynamic work counter of the K/V kernel
   kPlanHidCounter = 3,    // reserved
-  kPlanStatus = 4,        // non-zero when a kernel gave up on a bounded wait
+  kPlanStatus = 4,        // device status of the last call that used this scratch (StatusCode)
   kPlanNumHidSubs = 5,    // 16-row sub-blocks in the hidden requests' tile list (incl. padding entries)
   kPlanStatsWord = 16,    // 8 x 64-bit cycle counters of the re-projection kernel (debug aid), then
                           // one more: SM cycles its CTA 0 spent in the last launch
   kPlanWords = 64
+};
+
+// Values of the status word.  1..7: a bounded mbarrier wait of the re-projection kernel ran
+// out (the code names the waiting role); the combine kernel then fills the whole output with
+// NaN.  8: the batch holds K/V-cached requests but the call was given no K/V cache; their
+// output rows are zero, the hidden-cached requests' rows are valid.
+enum StatusCode {
+  kStatusOk = 0,
+  kStatusWaitFirst = 1,
+  kStatusWaitLast = 7,
+  kStatusNoKvCache = 8
 };
 
 struct WorkspaceLayout {
@@ -102,9 +113,11 @@ struct AttnShape {
 // starts a new tile (tile = 128-token chunk, hid_tiles is filled too); pack_tiles = true:
 // the sub-blocks of consecutive hidden requests are packed back to back, so a tile can hold
 // rows of several requests and only the last tile is partly empty.
+// kv_present = false: the call has no K/V cache; K/V-cached requests then get no work and no
+// partials (zero output rows) and the status word is set to kStatusNoKvCache.
 int launch_plan(const WorkspacePtrs& ws, const int32_t* seq_lens, const int32_t* cache_type,
                 const int32_t* block_tables, int batch, int max_blocks_per_seq, int block_size,
-                bool pack_tiles, cudaStream_t stream);
+                bool pack_tiles, bool kv_present, cudaStream_t stream);
 
 int launch_kv_attention(const WorkspacePtrs& ws, const void* query, const void* key_cache,
                         const void* value_cache, const int32_t* block_tables,
@@ -132,5 +145,29 @@ struct SimtHiddenArgs {
 };
 bool hidden_simt_supported(int dtype, int head_size);
 int launch_hidden_simt(const WorkspacePtrs& ws, const SimtHiddenArgs& a, cudaStream_t stream);
+
+// One hybrid decode attention call (the arguments of aps_hybrid_decode_attention).
+struct HybridCall {
+  AttnShape shape;
+  void* out; const void* query; const void* key_cache; const void* value_cache;
+  const void* hidden_cache; const void* w_k; const void* b_k; const void* w_v; const void* b_v;
+  const int32_t* block_tables; const int32_t* seq_lens; const int32_t* cache_type;
+  int hidden_size;
+  int64_t hidden_row_stride, num_hidden_rows, w_stride;
+  void* workspace; size_t workspace_bytes;
+};
+// New-token cache writes of a decode batch addressed from the block tables (cache_ops.cu).
+// key == NULL: no K/V rows are written; hidden == NULL: no hidden rows are written.
+struct NewTokenWrite {
+  const void* hidden; const void* key; const void* value; void* key_cache; void* value_cache; void* hidden_cache;
+  const int32_t* block_tables; const int32_t* seq_lens; const int32_t* cache_type;
+  int batch, max_blocks_per_seq, block_size, heads, head_size, hidden_size;
+  int64_t hidden_stride, key_stride, value_stride, block_stride, slot_stride;
+  int dtype;
+};
+int launch_new_token_write(const NewTokenWrite& a, cudaStream_t stream);
+
+int check_hybrid_call(const char* op, const HybridCall& c);
+int enqueue_hybrid_attention(const HybridCall& c, cudaStream_t stream);
 
 }  // namespace aps

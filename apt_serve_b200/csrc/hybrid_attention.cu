@@ -30,21 +30,17 @@
 //             shuffles and merged per request segment; one (max, sum, acc[128]) partial
 //             per (segment, head) goes to scratch.
 //
-// Two variants of the main loop:
-//   pair     (default) two CTAs of a cluster (cta_group::2) work on two M tiles of the
-//            same head with one M256 N256 instruction stream issued by the even CTA:
-//            each CTA loads its own X tile and HALF of the W rows (even CTA: W_k,h,
-//            odd CTA: W_v,h), the tensor cores read both halves, 6 stages of 32 KB.
-//            Loads carry no multicast: each CTA fetches what it needs itself; the two
-//            CTAs only exchange mbarrier arrivals.
-//   single   one CTA per SM works alone: M128 N256 instructions, both W boxes
-//            loaded by the CTA, 4 stages of 48 KB.
+// Main loop: two CTAs of a cluster (cta_group::2) work on two M tiles of the same head
+// with one M256 N256 instruction stream issued by the even CTA: each CTA loads its own X
+// tile and HALF of the W rows (even CTA: W_k,h, odd CTA: W_v,h), the tensor cores read both
+// halves, 6 stages of 32 KB.  Loads carry no multicast: each CTA fetches what it needs
+// itself; the two CTAs only exchange mbarrier arrivals.
 // CTAs are persistent and walk the items in groups (a few M tiles x a few heads) so
 // that hidden tiles and W slabs are shared through L2.
 //
-// Environment knobs (read at call time): APS_HIDDEN_VARIANT=single|pair,
-// APS_RASTER=units,heads, APS_PACK_TILES=0, APS_SPLIT_ISSUE=0, APS_STATS=1 (cycle counters
-// in the scratch header), APS_FORCE_SIMT=1, APS_DENSE_A=0.
+// The library reads no environment variable.  Building with -DAPS_TUNING adds one
+// (APS_RASTER=units,heads: group sizes of the work order) for sweeps; the default build
+// has none.
 //
 // Every mbarrier wait is bounded by a clock budget; a wait that runs out records
 // a code in the plan's status word, tells the other warps through shared memory,
@@ -69,22 +65,14 @@ constexpr int kSubRows = 16;                     // rows per TMA box of the hidd
 constexpr int kSubBytes = kSubRows * kBKBytes;   // 2 KB
 constexpr int kSubsPerTile = kBM / kSubRows;     // 8
 constexpr int kThreads = 320;          // warps 0 and 6-9 TMA producers, 1 MMA issue, 2-5 epilogue
-constexpr int kMaxStages = 6;
+constexpr int kStages = 6;
+constexpr int kBBytes = kBN / 2 * kBKBytes;      // 16 KB: this CTA's half of the W rows
+constexpr int kStageBytes = kABytes + kBBytes;   // 32 KB
 constexpr long long kWaitBudget = 4000000000LL;  // clock cycles (~2 s) before a wait gives up
 
-template <bool PAIR> struct Variant;
-template <> struct Variant<false> {
-  static constexpr int kStages = 4;
-  static constexpr int kBBytes = kBN * kBKBytes;       // 32 KB: W_k,h and W_v,h rows
-};
-template <> struct Variant<true> {
-  static constexpr int kStages = 6;
-  static constexpr int kBBytes = kBN / 2 * kBKBytes;   // 16 KB: this CTA's half of the W rows
-};
-
 struct SmemAux {
-  uint64_t full[kMaxStages];
-  uint64_t empty[kMaxStages];
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
   uint32_t tmem_base;
@@ -103,10 +91,8 @@ struct SmemAux {
   alignas(16) float red_acc[kSubsPerTile][kHeadDim];   // written as float2
 };
 
-template <bool PAIR>
 constexpr size_t smem_bytes() {
-  return 1024 /*alignment slack*/ +
-         (size_t)Variant<PAIR>::kStages * (kABytes + Variant<PAIR>::kBBytes) + sizeof(SmemAux);
+  return 1024 /*alignment slack*/ + (size_t)kStages * kStageBytes + sizeof(SmemAux);
 }
 
 // ---- PTX wrappers --------------------------------------------------------------
@@ -116,17 +102,11 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
 }
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
 __device__ __forceinline__ void mbar_expect_tx_addr(uint32_t bar_addr, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_addr), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_addr(uint32_t bar_addr) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_addr) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 // Arrive on a barrier given by its shared::cluster address (own CTA or the peer).
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
@@ -141,19 +121,17 @@ __device__ __forceinline__ bool mbar_try_wait_addr(uint32_t bar_addr, uint32_t p
       : "=r"(ok) : "r"(bar_addr), "r"(parity) : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  return mbar_try_wait_addr(smem_u32(bar), parity);
-}
-// Bounded wait.  Returns false when it gave up (or another warp already did).
+// Bounded wait.  Returns false when it gave up (or another warp already did): the code goes
+// to the CTA's abort flag and, first come first served, to the status word in global memory.
 __device__ __forceinline__ bool mbar_wait_addr(uint32_t bar_addr, uint32_t parity, volatile int* abort_flag,
-                                               int* status, int code) {
+                                               int* status, int code, long long budget = kWaitBudget) {
   if (mbar_try_wait_addr(bar_addr, parity)) return true;
   const long long t0 = clock64();
   int spins = 0;
   while (!mbar_try_wait_addr(bar_addr, parity)) {
     if ((++spins & 255) == 0) {
       if (*abort_flag != 0) return false;
-      if (clock64() - t0 > kWaitBudget) {
+      if (clock64() - t0 > budget) {
         *abort_flag = code;
         if (status != nullptr) atomicCAS(status, 0, code);
         return false;
@@ -194,68 +172,32 @@ __device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t rank) {
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// Tensor copies (TMA): a box of the tensor map lands in this CTA's shared memory, the bytes
-// are counted on an mbarrier.  The pair form may name a barrier of the peer CTA (given as a
-// shared::cluster address).  Destination and barrier are 32-bit shared addresses.
-__device__ __forceinline__ void tma_load_2d_a(uint32_t smem_dst, const CUtensorMap* map, uint32_t bar,
-                                              int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void tma_load_2d_pair_a(uint32_t smem_dst, const CUtensorMap* map,
-                                                   uint32_t bar_cluster_addr, int x, int y) {
+// Tensor copy (TMA): a box of the tensor map lands in this CTA's shared memory, the bytes
+// are counted on an mbarrier of the even CTA of the pair (given as a shared::cluster address).
+// Destination and barrier are 32-bit shared addresses.  No multicast: one destination CTA.
+__device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap* map,
+                                            uint32_t bar_cluster_addr, int x, int y) {
   asm volatile(
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y) : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-// Pair variant: the barrier is named by a shared::cluster address (own CTA or peer).
-__device__ __forceinline__ void tc_commit_pair(uint32_t bar_cluster_addr) {
+// The barrier is named by a shared::cluster address (own CTA or peer).
+__device__ __forceinline__ void tc_commit(uint32_t bar_cluster_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
-__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+// One M256 N256 K16 instruction of the CTA pair.  The operand descriptors are given as 32-bit
+// halves (the high half is common to both operands): the issuing thread steps a descriptor
+// with one 32-bit add.
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi,
                                            uint32_t idesc, uint32_t accumulate) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-// The same with the descriptors given as 32-bit halves (the high half is common to both
-// operands): the issuing thread then steps a descriptor with one 32-bit add.
-template <bool PAIR>
-__device__ __forceinline__ void tc_mma_f16_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi,
-                                              uint32_t idesc, uint32_t accumulate) {
-  if (PAIR)
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
-        "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
-        "setp.ne.b32 p, %5, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate) : "memory");
-  else
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
-        "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
-        "setp.ne.b32 p, %5, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tc_commit_addr(uint32_t bar_addr) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_addr) : "memory");
-}
-__device__ __forceinline__ void tc_mma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                                uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
   asm volatile(
@@ -283,12 +225,12 @@ __device__ __forceinline__ bool epi_all(bool flag) {
   return out != 0;
 }
 
-// K-major operand tile with 128-byte swizzle: rows of 128 bytes, 8-row groups
-// 1024 bytes apart (SBO), descriptor version 1, layout type 2 (SWIZZLE_128B).
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
-  const uint32_t lo = ((smem_addr & 0x3FFFFu) >> 4) | (1u << 16);
-  const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
-  return (static_cast<uint64_t>(hi) << 32) | lo;
+// Shared-memory operand descriptor of a K-major tile with 128-byte swizzle (rows of 128 bytes,
+// 8-row groups 1024 bytes apart): low half = (address >> 4) | version 1 in bit 16, high half =
+// stride byte offset 1024 >> 4, bit 14, layout type 2 (SWIZZLE_128B) in bits 29-31.
+constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t smem_addr) {
+  return ((smem_addr & 0x3FFFFu) >> 4) | (1u << 16);
 }
 
 // kind::f16 instruction descriptor: fp32 accumulate, A/B format fmt (0 = f16,
@@ -330,15 +272,13 @@ struct HiddenParams {
   int raster_units;           // units per group of the work order (see item_of)
   int raster_heads;           // heads per group of the work order
   int dense_a;                // X rows of a tile are contiguous: map_x has a 128-row box
-  int split_issue;            // the boxes of a stage are issued by four producer threads
-  unsigned long long* stats;  // optional cycle counters (nullptr = off): see aps_hybrid_decode_attention
   int* status;
 };
 
-struct Item { int unit, head; };   // unit = M tile (single) or tile pair (pair variant)
+struct Item { int unit, head; };   // unit = a pair of M tiles (2u, 2u + 1)
 
-// Work order.  Heads are taken in groups of `rh`; inside a head group the units (M tiles
-// or tile pairs) are taken in groups of `ru`; inside such a block the order is head-major.
+// Work order.  Heads are taken in groups of `rh`; inside a head group the units (tile
+// pairs) are taken in groups of `ru`; inside such a block the order is head-major.
 // While a head group is being worked on its W rows (rh x 2 x 128 x E elements) stay hot in
 // L2 across all unit groups, and the hidden rows of a unit group are fetched from HBM once
 // per head group and reused from L2 by the group's other heads.
@@ -559,125 +499,70 @@ __device__ __forceinline__ void epilogue_compute(SmemAux* aux, const HiddenParam
 // ---- TMA producer role -----------------------------------------------------------
 // Issuing one tensor copy costs the issuing thread on the order of a hundred cycles
 // whatever the size of the box, and a paged tile needs eight 16-row boxes plus the W
-// boxes per 64-element slab: one thread cannot issue them within the 512 cycles the
+// box per 64-element slab: one thread cannot issue them within the 512 cycles the
 // tensor cores need for the slab.  So the boxes of a stage are split over five producer
 // threads in five warps.  Producer 0 (warp 0) posts the stage's byte count and issues the
-// W boxes; producers 1..4 (warps 6..9) issue two cache blocks of the tile each.  Every
-// producer waits for the stage to be free on its own.
-template <typename T, int MODE, bool PAIR, bool STATS>
+// W box (and the one 128-row box of a dense X tile); producers 1..4 (warps 6..9) own two
+// fixed block slots of the tile each, so a producer's loop holds at most two copy
+// instructions (a copy that is predicated off still costs the thread some twenty cycles).
+// Every producer waits for the stage to be free on its own.  Like the MMA issuer, a producer
+// is one thread with a few hundred cycles per slab: addresses are stepped, not recomputed
+// from the stage index.
+template <typename T, int MODE>
 __device__ __forceinline__ void tma_producer(const HiddenParams& p, SmemAux* aux, uint8_t* smem,
                                              const CUtensorMap& map_x, const CUtensorMap& map_wk,
                                              const CUtensorMap& map_wv, int prod, int n_tiles,
                                              int n_units, int n_items, int first, int stride,
                                              uint32_t rank) {
-  using V = Variant<PAIR>;
-  constexpr int kStages = V::kStages;
-  constexpr int kStageBytes = kABytes + V::kBBytes;
   volatile int* abort_flag = &aux->abort_flag;
   const bool leader = rank == 0;
-  const bool split = p.split_issue != 0;   // else producer 0 issues everything
-  if (!split && prod != 0) return;
+  const bool dense = p.dense_a != 0;
   uint32_t stage = 0, phase = 0;
   bool ok = true;
-  long long w_empty = 0, w_issue = 0;
-  const long long p_begin = (STATS && p.stats && prod == 0) ? clock64() : 0;
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t full_base = smem_u32(&aux->full[0]);
+  const uint32_t empty_base = smem_u32(&aux->empty[0]);
+  const uint32_t bar_first = mapa_u32(full_base, 0);   // where the bytes are counted: the even CTA
+  const int j0 = prod > 0 ? (prod - 1) * 2 : kSubsPerTile;   // producer 0 owns no block slot
+  const uint32_t sub_off = (uint32_t)(j0 * kSubBytes);
+  const CUtensorMap* w_map = leader ? &map_wk : &map_wv;
   for (int i = first; i < n_items && ok; i += stride) {
     const Item it = item_of(i, n_units, p.heads, p.raster_units, p.raster_heads);
-    const int tile = PAIR ? it.unit * 2 + (int)rank : it.unit;
+    const int tile = it.unit * 2 + (int)rank;
     const int n_sub = tile_n_sub<MODE>(p, tile, n_tiles);
     int sub_row[kSubsPerTile];
     tile_sub_rows<MODE>(p, n_sub > 0 ? tile : 0, n_sub, sub_row);
     // a dense X tile is one 128-row box (rows past the end are zero-filled and still
     // counted); a paged tile is one 16-row box per cache block in use
-    const bool dense = p.dense_a != 0;
-    uint32_t tx_bytes = (uint32_t)((dense ? (n_sub > 0 ? kABytes : 0) : n_sub * kSubBytes) + V::kBBytes);
-    if (PAIR && leader) {
+    uint32_t tx_bytes = (uint32_t)((dense ? (n_sub > 0 ? kABytes : 0) : n_sub * kSubBytes) + kBBytes);
+    if (leader) {
       const int peer_sub = tile_n_sub<MODE>(p, tile + 1, n_tiles);
-      tx_bytes += (uint32_t)((dense ? (peer_sub > 0 ? kABytes : 0) : peer_sub * kSubBytes) + V::kBBytes);
+      tx_bytes += (uint32_t)((dense ? (peer_sub > 0 ? kABytes : 0) : peer_sub * kSubBytes) + kBBytes);
     }
-    // the boxes this producer issues.  With the split, a producer owns two fixed block
-    // slots, so its loop holds at most four copy instructions (a copy instruction that is
-    // predicated off still costs the thread some twenty cycles).
-    const bool do_w0 = prod == 0;                         // W_k (single) / this CTA's half (pair)
-    const bool do_w1 = !PAIR && prod == 0;                // W_v (single)
+    const bool do_w = prod == 0;
     const bool do_dense = dense && prod == 0 && n_sub > 0;
-    const bool post = prod == 0 && (!PAIR || leader);                  // posts the stage's byte count
-    const CUtensorMap* w0_map = PAIR ? (leader ? &map_wk : &map_wv) : &map_wk;
+    const bool post = prod == 0 && leader;            // posts the stage's byte count
     const int hrow = it.head * kHeadDim;
-    const uint32_t smem_base = smem_u32(smem);
-    const uint32_t full_base = smem_u32(&aux->full[0]);
-    if (split) {
-      const int j0 = prod > 0 ? (prod - 1) * 2 : kSubsPerTile;   // producer 0 issues the W boxes only
-      int r0 = 0, r1 = 0;
+    int r0 = 0, r1 = 0;
 #pragma unroll
-      for (int j = 0; j < kSubsPerTile; ++j) { if (j == j0) r0 = sub_row[j]; if (j == j0 + 1) r1 = sub_row[j]; }
-      const bool has0 = !dense && j0 < n_sub, has1 = !dense && j0 + 1 < n_sub;
-      // like the MMA issuer, a producer is one thread with a few hundred cycles per slab:
-      // addresses are stepped, not recomputed from the stage index
-      const uint32_t sub_off = (uint32_t)(j0 * kSubBytes);
-      const uint32_t bar_first = PAIR ? mapa_u32(full_base, 0) : full_base;   // where the bytes are counted
-      const uint32_t empty_base = smem_u32(&aux->empty[0]);
-      uint32_t a_dst = smem_base + stage * kStageBytes, off8 = stage * 8;
-      int x = 0;
-      for (int ks = p.k_slabs; ks > 0; --ks) {
-        const long long t0 = (STATS && p.stats && prod == 0) ? clock64() : 0;
-        if (!mbar_wait_addr(empty_base + off8, phase ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
-        const long long t1 = (STATS && p.stats && prod == 0) ? clock64() : 0;
-        const uint32_t b_dst = a_dst + kABytes;
-        const uint32_t bar = bar_first + off8;
-        if (post) mbar_expect_tx_addr(full_base + off8, tx_bytes);
-        if (PAIR) {
-          if (do_dense) tma_load_2d_pair_a(a_dst, &map_x, bar, x, tile * kBM);
-          if (has0) tma_load_2d_pair_a(a_dst + sub_off, &map_x, bar, x, r0);
-          if (has1) tma_load_2d_pair_a(a_dst + sub_off + kSubBytes, &map_x, bar, x, r1);
-          if (prod != 0) mbar_arrive_addr(full_base + off8);
-          else if (!leader && !mbar_wait_addr(full_base + off8, phase, abort_flag, p.status, 6)) { ok = false; break; }
-          if (do_w0) tma_load_2d_pair_a(b_dst, w0_map, bar, x, hrow);
-        } else {
-          if (do_dense) tma_load_2d_a(a_dst, &map_x, bar, x, tile * kBM);
-          if (has0) tma_load_2d_a(a_dst + sub_off, &map_x, bar, x, r0);
-          if (has1) tma_load_2d_a(a_dst + sub_off + kSubBytes, &map_x, bar, x, r1);
-          if (do_w0) tma_load_2d_a(b_dst, w0_map, bar, x, hrow);
-          if (do_w1) tma_load_2d_a(b_dst + V::kBBytes / 2, &map_wv, bar, x, hrow);
-          if (prod != 0) mbar_arrive_addr(bar);
-        }
-        if (STATS && p.stats && prod == 0) { w_empty += t1 - t0; w_issue += clock64() - t1; }
-        x += kBKBytes / (int)sizeof(T);
-        a_dst += kStageBytes; off8 += 8;
-        if (++stage == kStages) { stage = 0; phase ^= 1; a_dst = smem_base; off8 = 0; }
-      }
-    } else {
-      for (int ks = 0; ks < p.k_slabs; ++ks) {
-        const long long t0 = (STATS && p.stats && prod == 0) ? clock64() : 0;
-        if (!mbar_wait(&aux->empty[stage], phase ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
-        const long long t1 = (STATS && p.stats && prod == 0) ? clock64() : 0;
-        const uint32_t a_dst = smem_base + stage * kStageBytes;
-        const uint32_t b_dst = a_dst + kABytes;
-        const uint32_t bar_local = full_base + stage * 8;
-        const int x = ks * (kBKBytes / (int)sizeof(T));
-        if (post) mbar_expect_tx(&aux->full[stage], tx_bytes);
-        if (PAIR) {
-          const uint32_t bar = mapa_u32(bar_local, 0);
-          if (do_dense) tma_load_2d_pair_a(a_dst, &map_x, bar, x, tile * kBM);
-          if (!dense) {
-#pragma unroll
-            for (int j = 0; j < kSubsPerTile; ++j)
-              if (j < n_sub) tma_load_2d_pair_a(a_dst + j * kSubBytes, &map_x, bar, x, sub_row[j]);
-          }
-          if (do_w0) tma_load_2d_pair_a(b_dst, w0_map, bar, x, hrow);
-        } else {
-          if (do_dense) tma_load_2d_a(a_dst, &map_x, bar_local, x, tile * kBM);
-          if (!dense) {
-#pragma unroll
-            for (int j = 0; j < kSubsPerTile; ++j)
-              if (j < n_sub) tma_load_2d_a(a_dst + j * kSubBytes, &map_x, bar_local, x, sub_row[j]);
-          }
-          if (do_w0) tma_load_2d_a(b_dst, w0_map, bar_local, x, hrow);
-          if (do_w1) tma_load_2d_a(b_dst + V::kBBytes / 2, &map_wv, bar_local, x, hrow);
-        }
-        if (STATS && p.stats && prod == 0) { w_empty += t1 - t0; w_issue += clock64() - t1; }
-        if (++stage == kStages) { stage = 0; phase ^= 1; }
-      }
+    for (int j = 0; j < kSubsPerTile; ++j) { if (j == j0) r0 = sub_row[j]; if (j == j0 + 1) r1 = sub_row[j]; }
+    const bool has0 = !dense && j0 < n_sub, has1 = !dense && j0 + 1 < n_sub;
+    uint32_t a_dst = smem_base + stage * kStageBytes, off8 = stage * 8;
+    int x = 0;
+    for (int ks = p.k_slabs; ks > 0; --ks) {
+      if (!mbar_wait_addr(empty_base + off8, phase ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
+      const uint32_t b_dst = a_dst + kABytes;
+      const uint32_t bar = bar_first + off8;
+      if (post) mbar_expect_tx_addr(full_base + off8, tx_bytes);
+      if (do_dense) tma_load_2d(a_dst, &map_x, bar, x, tile * kBM);
+      if (has0) tma_load_2d(a_dst + sub_off, &map_x, bar, x, r0);
+      if (has1) tma_load_2d(a_dst + sub_off + kSubBytes, &map_x, bar, x, r1);
+      if (prod != 0) mbar_arrive_addr(full_base + off8);
+      else if (!leader && !mbar_wait_addr(full_base + off8, phase, abort_flag, p.status, 6)) { ok = false; break; }
+      if (do_w) tma_load_2d(b_dst, w_map, bar, x, hrow);
+      x += kBKBytes / (int)sizeof(T);
+      a_dst += kStageBytes; off8 += 8;
+      if (++stage == kStages) { stage = 0; phase ^= 1; a_dst = smem_base; off8 = 0; }
     }
   }
   if (!ok) {
@@ -686,22 +571,13 @@ __device__ __forceinline__ void tma_producer(const HiddenParams& p, SmemAux* aux
     const long long t0 = clock64();
     while (clock64() - t0 < 2000000LL) { }
   }
-  if (STATS && p.stats && prod == 0) {
-    atomicAdd(p.stats + 3, (unsigned long long)w_empty);
-    atomicAdd(p.stats + 4, (unsigned long long)(clock64() - p_begin));
-    atomicAdd(p.stats + 5, (unsigned long long)w_issue);
-  }
 }
 
 // ---- the kernel ---------------------------------------------------------------------
-template <typename T, int MODE, bool PAIR, bool STATS>
+template <typename T, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_wk,
                    const __grid_constant__ CUtensorMap map_wv, const HiddenParams p) {
-  using V = Variant<PAIR>;
-  constexpr int kStages = V::kStages;
-  constexpr int kStageBytes = kABytes + V::kBBytes;
-
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   SmemAux* aux = reinterpret_cast<SmemAux*>(smem + (size_t)kStages * kStageBytes);
@@ -710,105 +586,84 @@ hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
   const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
   const long long kernel_begin = clock64();
   volatile int* abort_flag = &aux->abort_flag;
-  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;   // position in the CTA pair
+  const uint32_t rank = cluster_ctarank();   // position in the CTA pair
   const bool leader = rank == 0;
 
   if (threadIdx.x == 0) {
-    // full[s]: one arrival from producer 0 (with the byte count of the stage's boxes), plus one
-    // per slab from each of this CTA's producers 1..4 when the boxes are split.  The last are
-    // what keeps a producer without boxes in this tile in step: a stage cannot fill, be
-    // consumed and be freed again behind the back of a producer that is still waiting for it
-    // (a parity wait that is lapped twice never returns).  In the odd CTA of a pair, whose
-    // bytes are counted on the even CTA's barrier, full[s] takes only those four arrivals and
-    // its producer 0 waits for them before it issues the stage's W box (an arrival on the
-    // peer's barrier per slab and producer costs ~2000 cycles).
-    const bool split_on = p.split_issue != 0;
-    const uint32_t full_count = (PAIR && cluster_ctarank() != 0) ? (split_on ? 4u : 1u)
-                                                                 : 1u + (split_on ? 4u : 0u);
+    // full[s] of the even CTA: one arrival from its producer 0 (with the byte count of both
+    // CTAs' boxes) plus one per slab from each of its producers 1..4.  The last are what keeps
+    // a producer without boxes in this tile in step: a stage cannot fill, be consumed and be
+    // freed again behind the back of a producer that is still waiting for it (a parity wait
+    // that is lapped twice never returns).  In the odd CTA, whose bytes are counted on the even
+    // CTA's barrier, full[s] takes only those four arrivals and its producer 0 waits for them
+    // before it issues the stage's W box (an arrival on the peer's barrier per slab and
+    // producer costs ~2000 cycles).
+    const uint32_t full_count = leader ? 5u : 4u;
     for (int s = 0; s < kStages; ++s) { mbar_init(&aux->full[s], full_count); mbar_init(&aux->empty[s], 1); }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&aux->acc_full[b], 1);
-      mbar_init(&aux->acc_empty[b], PAIR ? 8 : 4);   // one arrival per epilogue warp (of both CTAs)
+      mbar_init(&aux->acc_empty[b], 8);   // one arrival per epilogue warp of both CTAs
     }
     aux->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    if (PAIR) {
-      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(&aux->tmem_base)) : "memory");
-      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-    } else {
-      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(&aux->tmem_base)) : "memory");
-      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(&aux->tmem_base)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
   __syncthreads();
-  if (PAIR) cluster_sync_all();   // the peer's barriers are initialised before anyone signals them
+  cluster_sync_all();   // the peer's barriers are initialised before anyone signals them
   tc_fence_after();
   const uint32_t tmem_base = aux->tmem_base;
 
   const int n_tiles = MODE == kModeAttend ? p.plan[kPlanNumHidTiles] : p.n_store_tiles;
-  const int n_units = PAIR ? (n_tiles + 1) / 2 : n_tiles;
+  const int n_units = (n_tiles + 1) / 2;
   const int n_items = n_units * p.heads;
-  const int first = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
-  const int stride = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  const int first = (int)(blockIdx.x >> 1);
+  const int stride = (int)(gridDim.x >> 1);
 
   if (warp == 0) {
     // ===================== TMA producer 0 =====================
     if (lane == 0)
-      tma_producer<T, MODE, PAIR, STATS>(p, aux, smem, map_x, map_wk, map_wv, 0, n_tiles, n_units, n_items,
-                                  first, stride, rank);
+      tma_producer<T, MODE>(p, aux, smem, map_x, map_wk, map_wv, 0, n_tiles, n_units, n_items, first, stride, rank);
     __syncwarp();
   } else if (warp == 1) {
-    // ===================== MMA issuer (the even CTA of a pair issues for both) =====================
+    // ===================== MMA issuer (the even CTA issues for both) =====================
     if (leader) {
       // The whole warp runs the loop (waits, address stepping) in step and one elected lane
       // issues the tensor-core instructions: their operands are then warp-uniform values the
       // compiler can keep in uniform registers.  The issuer has 512 cycles per slab and a
       // lone warp issues an instruction only every few cycles, so everything the loop needs
       // is a 32-bit register stepped by a constant (barrier addresses, the low halves of the
-      // two operand descriptors), nothing is recomputed from the stage index, and the cycle
-      // counters are compiled out unless asked for.
+      // two operand descriptors) and nothing is recomputed from the stage index.
       const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
-      const uint32_t idesc = instr_desc(fmt, PAIR ? 256u : 128u);
-      constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);   // see smem_desc_sw128
+      const uint32_t idesc = instr_desc(fmt, 256u);
       constexpr uint32_t kDescStep = (uint32_t)kStageBytes >> 4, kDescB = (uint32_t)kABytes >> 4;
-      const uint32_t a_lo_first = ((smem_u32(smem) & 0x3FFFFu) >> 4) | (1u << 16);
-      const uint32_t a_lo_end = a_lo_first + kStages * kDescStep;
+      const uint32_t a_lo_first = smem_desc_lo(smem_u32(smem));
       const uint32_t full_first = smem_u32(&aux->full[0]), full_end = full_first + kStages * 8;
-      const uint32_t empty_own = PAIR ? mapa_u32(smem_u32(&aux->empty[0]), 0) : smem_u32(&aux->empty[0]);
-      const uint32_t peer_delta = PAIR ? mapa_u32(smem_u32(&aux->empty[0]), 1) - empty_own : 0u;
+      const uint32_t empty_own = mapa_u32(smem_u32(&aux->empty[0]), 0);
+      const uint32_t peer_delta = mapa_u32(smem_u32(&aux->empty[0]), 1) - empty_own;
       uint32_t a_lo = a_lo_first, full_addr = full_first, empty_addr = empty_own, phase = 0, n_local = 0;
       bool ok = true;
-      const bool st = STATS && p.stats != nullptr;
-      long long t_begin = st ? clock64() : 0, w_full = 0, w_acc = 0, w_first = 0;
       for (int i = first; i < n_items && ok; i += stride, ++n_local) {
         const uint32_t buf = n_local & 1u, use = n_local >> 1;
-        long long t0 = st ? clock64() : 0;
         if (!mbar_wait_warp(smem_u32(&aux->acc_empty[buf]), (use & 1u) ^ 1u, abort_flag, p.status, 2, lane)) { ok = false; break; }
-        if (st) w_acc += clock64() - t0;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * kBN;
         uint32_t accumulate = 0;
         for (int ks = p.k_slabs; ks > 0; --ks) {
-          if (st) t0 = clock64();
           if (!mbar_wait_warp(full_addr, phase, abort_flag, p.status, 3, lane)) { ok = false; break; }
-          if (st) { const long long dt = clock64() - t0; w_full += dt; if (ks == p.k_slabs) w_first += dt; }
           tc_fence_after();
           if (elect_one()) {
             const uint32_t b_lo = a_lo + kDescB;
-            tc_mma_f16_lo<PAIR>(d_tmem, a_lo, b_lo, kDescHi, idesc, accumulate);
-            tc_mma_f16_lo<PAIR>(d_tmem, a_lo + 2, b_lo + 2, kDescHi, idesc, 1u);
-            tc_mma_f16_lo<PAIR>(d_tmem, a_lo + 4, b_lo + 4, kDescHi, idesc, 1u);
-            tc_mma_f16_lo<PAIR>(d_tmem, a_lo + 6, b_lo + 6, kDescHi, idesc, 1u);
-            if (PAIR) {
-              tc_commit_pair(empty_addr);                 // release the stage in both CTAs
-              tc_commit_pair(empty_addr + peer_delta);
-            } else {
-              tc_commit_addr(empty_addr);
-            }
+            tc_mma_f16(d_tmem, a_lo, b_lo, kDescHi, idesc, accumulate);
+            tc_mma_f16(d_tmem, a_lo + 2, b_lo + 2, kDescHi, idesc, 1u);
+            tc_mma_f16(d_tmem, a_lo + 4, b_lo + 4, kDescHi, idesc, 1u);
+            tc_mma_f16(d_tmem, a_lo + 6, b_lo + 6, kDescHi, idesc, 1u);
+            tc_commit(empty_addr);                 // release the stage in both CTAs
+            tc_commit(empty_addr + peer_delta);
           }
           __syncwarp();
           accumulate = 1u;
@@ -818,31 +673,18 @@ hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
           }
         }
         if (ok && elect_one()) {
-          if (PAIR) {
-            const uint32_t f = smem_u32(&aux->acc_full[buf]);
-            tc_commit_pair(mapa_u32(f, 0));
-            tc_commit_pair(mapa_u32(f, 1));
-          } else {
-            tc_commit(&aux->acc_full[buf]);
-          }
+          const uint32_t f = smem_u32(&aux->acc_full[buf]);
+          tc_commit(mapa_u32(f, 0));
+          tc_commit(mapa_u32(f, 1));
         }
         __syncwarp();
-      }
-      (void)a_lo_end;
-      if (st && lane == 0) {
-        atomicAdd(p.stats + 0, (unsigned long long)(clock64() - t_begin));
-        atomicAdd(p.stats + 1, (unsigned long long)w_full);
-        atomicAdd(p.stats + 2, (unsigned long long)w_acc);
-        atomicAdd(p.stats + 6, (unsigned long long)n_local);
-        atomicAdd(p.stats + 7, (unsigned long long)w_first);
       }
     }
     __syncwarp();
   } else if (warp >= 6) {
     // ===================== TMA producers 1..4 (warps 6..9) =====================
     if (lane == 0)
-      tma_producer<T, MODE, PAIR, STATS>(p, aux, smem, map_x, map_wk, map_wv, warp - 5, n_tiles, n_units,
-                                         n_items, first, stride, rank);
+      tma_producer<T, MODE>(p, aux, smem, map_x, map_wk, map_wv, warp - 5, n_tiles, n_units, n_items, first, stride, rank);
     __syncwarp();
   } else {
     // ===================== epilogue (warps 2..5) =====================
@@ -852,30 +694,24 @@ hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     bool ok = true;
     for (int i = first; i < n_items && ok; i += stride, ++n_local) {
       const Item it = item_of(i, n_units, p.heads, p.raster_units, p.raster_heads);
-      const int tile = PAIR ? it.unit * 2 + (int)rank : it.unit;
+      const int tile = it.unit * 2 + (int)rank;
       const bool tile_ok = tile < n_tiles;
       const uint32_t buf = n_local & 1u, use = n_local >> 1;
       epilogue_stage_inputs<T, MODE>(aux, p, tile, tile_ok, it.head, et);
-      const long long t0 = (STATS && p.stats && et == 0) ? clock64() : 0;
       // one lane per warp polls the barrier; the other 124 threads wait in the hardware
       // barrier of epi_all (polling by every thread floods the SM's mbarrier unit and slows
       // the producer / MMA handshake down)
       const bool got = lane != 0 || mbar_wait(&aux->acc_full[buf], use & 1u, abort_flag, p.status, 4);
       if (!epi_all(got)) { ok = false; break; }
-      const long long t1 = (STATS && p.stats && et == 0) ? clock64() : 0;
       tc_fence_after();
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * kBN;
       uint64_t* acc_empty = &aux->acc_empty[buf];
       auto release = [&]() {
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) {
-          if (PAIR) mbar_arrive_cluster(mapa_u32(smem_u32(acc_empty), 0));
-          else mbar_arrive(acc_empty);
-        }
+        if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(acc_empty), 0));
       };
       epilogue_compute<T, MODE>(aux, p, t_row, tile, tile_ok, it.head, quarter, lane, et, release);
-      (void)t0; (void)t1;
     }
   }
 
@@ -884,13 +720,24 @@ hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
   // SM cycles CTA 0 spent in the kernel (always recorded: two clock reads per launch)
   if (MODE == kModeAttend && blockIdx.x == 0 && threadIdx.x == 0)
     reinterpret_cast<unsigned long long*>(p.plan + kPlanStatsWord)[8] = (unsigned long long)(clock64() - kernel_begin);
-  if (PAIR) cluster_sync_all();   // nobody leaves while the peer may still read its memory or signal it
+  cluster_sync_all();   // nobody leaves while the peer may still read its memory or signal it
   if (warp == 1) {
     tc_fence_after();
-    if (PAIR)
-      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
-    else
-      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+  }
+}
+
+// A bounded wait that runs out, on purpose and harmlessly: one thread waits on an mbarrier
+// nobody ever arrives on, for `budget` clock cycles, then records `code` in the status word
+// like the waits of hidden_path_kernel do.  Used by the tests of the status handling.
+__global__ void bounded_wait_selftest_kernel(int* status, long long budget, int code) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_wait_addr(smem_u32(&bar), 0, &abort_flag, status, code, budget);
   }
 }
 
@@ -912,9 +759,27 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// 2-D row-major matrix [rows, cols] of 2-byte elements, box [box_rows, 64 cols], 128-byte swizzle.
+// 2-D row-major matrix [rows, cols] of 2-byte elements, box [box_rows, 64 cols], 128-byte
+// swizzle.  A tensor map is a pure function of (base, dtype, shape, stride, box): the encoded
+// maps are kept in a small per-thread table, so a layer that is called every step with the
+// same cache and weights encodes its three maps once.
+struct MapKey {
+  const void* base; int dtype; uint64_t cols, rows, stride; uint32_t box_rows;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && dtype == o.dtype && cols == o.cols && rows == o.rows && stride == o.stride &&
+           box_rows == o.box_rows;
+  }
+};
+struct MapSlot { MapKey key; CUtensorMap map; bool used; };
+constexpr int kMapSlots = 32;
+
 int make_map(CUtensorMap* map, const void* base, int dtype, uint64_t cols, uint64_t rows,
              uint64_t row_stride_elems, uint32_t box_rows, const char* what) {
+  static thread_local MapSlot slots[kMapSlots] = {};
+  static thread_local unsigned next_slot = 0;
+  const MapKey key{base, dtype, cols, rows, row_stride_elems, box_rows};
+  for (int i = 0; i < kMapSlots; ++i)
+    if (slots[i].used && slots[i].key == key) { *map = slots[i].map; return APS_OK; }
   EncodeTiledFn fn = encode_fn();
   APS_REQUIRE(fn != nullptr, APS_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   const CUtensorMapDataType dt = dtype == APS_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -926,49 +791,54 @@ int make_map(CUtensorMap* map, const void* base, int dtype, uint64_t cols, uint6
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   APS_REQUIRE(r == CUDA_SUCCESS, APS_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, (int)r);
+  MapSlot& s = slots[next_slot++ % kMapSlots];
+  s.key = key; s.map = *map; s.used = true;
   return APS_OK;
 }
 
-// Which main-loop variant to run: APS_HIDDEN_VARIANT=single|pair overrides the default.
-bool use_pair_variant() {
-  const char* v = getenv("APS_HIDDEN_VARIANT");
-  if (v != nullptr && strcmp(v, "single") == 0) return false;
-  if (v != nullptr && strcmp(v, "pair") == 0) return true;
-  return true;
+// Work-order group sizes (tile pairs x heads).
+void raster_sizes(int* units, int* heads) {
+  *units = 8; *heads = 8;
+#ifdef APS_TUNING
+  const char* v = getenv("APS_RASTER");
+  if (v != nullptr) {
+    int a = 0, b = 0;
+    if (sscanf(v, "%d,%d", &a, &b) == 2 && a > 0 && b > 0) { *units = a; *heads = b; }
+  }
+#endif
 }
 
-template <typename T, int MODE, bool PAIR, bool STATS>
-int launch_hidden_variant(const CUtensorMap& mx, const CUtensorMap& mk, const CUtensorMap& mv,
-                          const HiddenParams& p, cudaStream_t stream) {
+// Launch geometry: one CTA per SM, in pairs, as many pairs as the device keeps resident at
+// once.  Looked up once per kernel instantiation and device (the library assumes one calling
+// thread per process, like the reference's single-threaded worker).
+template <typename T, int MODE>
+int launch_hidden(const CUtensorMap& mx, const CUtensorMap& mk, const CUtensorMap& mv,
+                  HiddenParams p, cudaStream_t stream) {
   static int grid_for_device[64] = {0};
+  raster_sizes(&p.raster_units, &p.raster_heads);
+  if (p.raster_heads > p.heads) p.raster_heads = p.heads;
   int dev = 0;
   APS_CUDA(cudaGetDevice(&dev));
   APS_REQUIRE(dev >= 0 && dev < 64, APS_ERR_CUDA, "device index %d out of range", dev);
-  auto kernel = hidden_path_kernel<T, MODE, PAIR, STATS>;
-  constexpr size_t smem = smem_bytes<PAIR>();
+  auto kernel = hidden_path_kernel<T, MODE>;
+  constexpr size_t smem = smem_bytes();
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
-  if (PAIR) {
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-  }
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
   if (grid_for_device[dev] == 0) {
     APS_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    int grid = sm_count();
-    if (PAIR) {
-      // one CTA per SM, in pairs: as many pairs as the device can keep resident at once
-      cfg.gridDim = dim3((unsigned)(grid & ~1));
-      int clusters = 0;
-      APS_CUDA(cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg));
-      APS_REQUIRE(clusters > 0, APS_ERR_CUDA, "no CTA pair of the re-projection kernel fits on this device");
-      grid = 2 * (clusters < grid / 2 ? clusters : grid / 2);
-    }
-    grid_for_device[dev] = grid;
+    const int sms = sm_count();
+    cfg.gridDim = dim3((unsigned)(sms & ~1));
+    int clusters = 0;
+    APS_CUDA(cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg));
+    APS_REQUIRE(clusters > 0, APS_ERR_CUDA, "no CTA pair of the re-projection kernel fits on this device");
+    grid_for_device[dev] = 2 * (clusters < sms / 2 ? clusters : sms / 2);
   }
   cfg.gridDim = dim3((unsigned)grid_for_device[dev]);
   {
@@ -978,32 +848,6 @@ int launch_hidden_variant(const CUtensorMap& mx, const CUtensorMap& mk, const CU
       return fail(APS_ERR_CUDA, "launch of hidden_path_kernel failed: %s", cudaGetErrorString(e));
   }
   return launch_status("hidden_path_kernel");
-}
-
-// Work-order group sizes: APS_RASTER="units,heads" overrides the default.
-void raster_sizes(int* units, int* heads) {
-  *units = 8; *heads = 8;
-  const char* v = getenv("APS_RASTER");
-  if (v != nullptr) {
-    int a = 0, b = 0;
-    if (sscanf(v, "%d,%d", &a, &b) == 2 && a > 0 && b > 0) { *units = a; *heads = b; }
-  }
-}
-
-template <typename T, int MODE>
-int launch_hidden(const CUtensorMap& mx, const CUtensorMap& mk, const CUtensorMap& mv,
-                  HiddenParams p, cudaStream_t stream) {
-  raster_sizes(&p.raster_units, &p.raster_heads);
-  if (p.raster_heads > p.heads) p.raster_heads = p.heads;
-  const char* si = getenv("APS_SPLIT_ISSUE");
-  p.split_issue = (si != nullptr && si[0] == '0') ? 0 : 1;
-  // the cycle counters are a separate instantiation of the attend kernel
-  if (MODE == kModeAttend && p.stats != nullptr)
-    return use_pair_variant() ? launch_hidden_variant<T, kModeAttend, true, true>(mx, mk, mv, p, stream)
-                              : launch_hidden_variant<T, kModeAttend, false, true>(mx, mk, mv, p, stream);
-  p.stats = nullptr;
-  return use_pair_variant() ? launch_hidden_variant<T, MODE, true, false>(mx, mk, mv, p, stream)
-                            : launch_hidden_variant<T, MODE, false, false>(mx, mk, mv, p, stream);
 }
 
 struct HiddenArgs {
@@ -1039,6 +883,72 @@ int make_maps(const HiddenArgs& a, CUtensorMap* mx, CUtensorMap* mk, CUtensorMap
 }
 
 }  // namespace
+
+// The hybrid decode attention after its arguments have been checked: plan, K/V streaming,
+// re-projection, combine, all on `cs`.
+int enqueue_hybrid_attention(const HybridCall& c, cudaStream_t cs) {
+  const AttnShape& s = c.shape;
+  int st;
+  HiddenArgs a{c.hidden_cache, c.w_k, c.b_k, c.w_v, c.b_v, s.heads, s.head_size, c.hidden_size,
+               c.hidden_row_stride, c.num_hidden_rows, c.w_stride, s.dtype};
+  // fp16 / bf16 with head size 128 run on the tensor cores; fp32 and head sizes 32 / 64 run
+  // the CUDA-core re-projection (same work items, same partials)
+  const bool tensor_path = (s.dtype == APS_F16 || s.dtype == APS_BF16) && s.head_size == kHeadDim;
+  CUtensorMap mx, mk, mv;
+  if (tensor_path) {
+    if ((st = check_hidden_args("hybrid_decode_attention", a)) != APS_OK) return st;
+    if ((st = make_maps(a, &mx, &mk, &mv)) != APS_OK) return st;
+  } else {
+    APS_REQUIRE(hidden_simt_supported(s.dtype, s.head_size), APS_ERR_UNSUPPORTED,
+                "hybrid_decode_attention: head size %d / dtype %d has no re-projection kernel "
+                "(tensor cores: fp16 or bf16 with head size 128; CUDA cores: head sizes 32, 64, 128)",
+                s.head_size, s.dtype);
+    APS_REQUIRE(c.hidden_cache && c.w_k && c.w_v, APS_ERR_NULL_POINTER, "hybrid_decode_attention: null pointer");
+    APS_REQUIRE(c.hidden_size > 0 && c.hidden_row_stride >= c.hidden_size && c.w_stride >= c.hidden_size,
+                APS_ERR_SHAPE, "hybrid_decode_attention: bad hidden sizes / strides");
+  }
+  const WorkspaceLayout w = workspace_layout(s.batch, s.max_blocks_per_seq, s.block_size, s.heads, s.head_size);
+  const WorkspacePtrs ws = workspace_ptrs(c.workspace, w);
+  const bool have_kv = c.key_cache != nullptr && c.value_cache != nullptr;
+  // the tensor-core kernel takes M tiles packed across requests, the CUDA-core kernel one
+  // request per tile
+  if ((st = launch_plan(ws, c.seq_lens, c.cache_type, c.block_tables, s.batch, s.max_blocks_per_seq,
+                        s.block_size, tensor_path, have_kv, cs)) != APS_OK) return st;
+  // K/V requests: on the call's stream before the re-projection kernel
+  if (have_kv) {
+    if ((st = launch_kv_attention(ws, c.query, c.key_cache, c.value_cache, c.block_tables, c.seq_lens, s, cs)) != APS_OK) return st;
+  }
+  if (!tensor_path) {
+    SimtHiddenArgs sa{c.query, c.hidden_cache, c.w_k, c.b_k, c.w_v, c.b_v, c.block_tables, c.seq_lens,
+                      s.max_blocks_per_seq, s.block_size, s.heads, s.head_size, c.hidden_size,
+                      s.query_stride, c.hidden_row_stride, c.w_stride, s.scale, s.dtype};
+    if ((st = launch_hidden_simt(ws, sa, cs)) != APS_OK) return st;
+    return launch_combine(ws, c.out, c.seq_lens, s, cs);
+  }
+  HiddenParams p{};
+  p.plan = ws.plan; p.part_offset = ws.part_offset; p.hid_subs = ws.hid_subs; p.first_tile = ws.first_tile; p.hid_rows = ws.hid_rows;
+  p.part_ml = ws.part_ml; p.part_acc = ws.part_acc; p.query = c.query;
+  p.block_tables = c.block_tables; p.seq_lens = c.seq_lens;
+  p.max_blocks_per_seq = s.max_blocks_per_seq; p.block_size = s.block_size;
+  p.query_stride = s.query_stride; p.scale_log2 = s.scale * 1.4426950408889634f;
+  p.b_k = c.b_k; p.b_v = c.b_v; p.heads = s.heads; p.k_slabs = (c.hidden_size + 63) / 64;
+  p.status = ws.plan + kPlanStatus;
+  st = s.dtype == APS_BF16 ? launch_hidden<__nv_bfloat16, kModeAttend>(mx, mk, mv, p, cs)
+                           : launch_hidden<__half, kModeAttend>(mx, mk, mv, p, cs);
+  if (st != APS_OK) return st;
+  return launch_combine(ws, c.out, c.seq_lens, s, cs);
+}
+
+int check_hybrid_call(const char* op, const HybridCall& c) {
+  int st = check_attention_args(op, c.out, c.query, c.key_cache, c.value_cache, c.block_tables, c.seq_lens,
+                                c.shape, c.workspace, c.workspace_bytes, false);
+  if (st != APS_OK || c.shape.batch == 0) return st;
+  APS_REQUIRE(c.cache_type != nullptr, APS_ERR_NULL_POINTER, "%s: cache_type is null", op);
+  APS_REQUIRE((c.key_cache == nullptr) == (c.value_cache == nullptr), APS_ERR_NULL_POINTER,
+              "%s: key_cache and value_cache must both be given or both be NULL", op);
+  return APS_OK;
+}
+
 }  // namespace aps
 
 using namespace aps;
@@ -1055,64 +965,18 @@ extern "C" int aps_hybrid_decode_attention(void* out, const void* query, const v
                                            int64_t num_hidden_rows, int64_t w_stride, float scale,
                                            void* workspace, size_t workspace_bytes, int dtype,
                                            void* stream) {
-  AttnShape s{batch, max_blocks_per_seq, num_heads, head_size, block_size,
-              query_stride, out_stride, block_stride, scale, dtype};
-  int st = check_attention_args("hybrid_decode_attention", out, query, key_cache, value_cache,
-                                block_tables, seq_lens, s, workspace, workspace_bytes, false);
+  HybridCall c{};
+  c.shape = AttnShape{batch, max_blocks_per_seq, num_heads, head_size, block_size,
+                      query_stride, out_stride, block_stride, scale, dtype};
+  c.out = out; c.query = query; c.key_cache = key_cache; c.value_cache = value_cache;
+  c.hidden_cache = hidden_cache; c.w_k = w_k; c.b_k = b_k; c.w_v = w_v; c.b_v = b_v;
+  c.block_tables = block_tables; c.seq_lens = seq_lens; c.cache_type = cache_type;
+  c.hidden_size = hidden_size; c.hidden_row_stride = hidden_row_stride;
+  c.num_hidden_rows = num_hidden_rows; c.w_stride = w_stride;
+  c.workspace = workspace; c.workspace_bytes = workspace_bytes;
+  int st = check_hybrid_call("hybrid_decode_attention", c);
   if (st != APS_OK || batch == 0) return st;
-  APS_REQUIRE(cache_type != nullptr, APS_ERR_NULL_POINTER, "hybrid_decode_attention: cache_type is null");
-  HiddenArgs a{hidden_cache, w_k, b_k, w_v, b_v, num_heads, head_size, hidden_size,
-               hidden_row_stride, num_hidden_rows, w_stride, dtype};
-  // fp16 / bf16 with head size 128 run on the tensor cores; fp32 and head sizes 32 / 64 run
-  // the CUDA-core re-projection (same work items, same partials)
-  const bool tensor_path = (dtype == APS_F16 || dtype == APS_BF16) && head_size == kHeadDim &&
-                           getenv("APS_FORCE_SIMT") == nullptr;
-  CUtensorMap mx, mk, mv;
-  if (tensor_path) {
-    if ((st = check_hidden_args("hybrid_decode_attention", a)) != APS_OK) return st;
-    if ((st = make_maps(a, &mx, &mk, &mv)) != APS_OK) return st;
-  } else {
-    APS_REQUIRE(hidden_simt_supported(dtype, head_size), APS_ERR_UNSUPPORTED,
-                "hybrid_decode_attention: head size %d / dtype %d has no re-projection kernel "
-                "(tensor cores: fp16 or bf16 with head size 128; CUDA cores: head sizes 32, 64, 128)",
-                head_size, dtype);
-    APS_REQUIRE(hidden_cache && w_k && w_v, APS_ERR_NULL_POINTER, "hybrid_decode_attention: null pointer");
-    APS_REQUIRE(hidden_size > 0 && hidden_row_stride >= hidden_size && w_stride >= hidden_size,
-                APS_ERR_SHAPE, "hybrid_decode_attention: bad hidden sizes / strides");
-  }
-
-  const WorkspaceLayout w = workspace_layout(batch, max_blocks_per_seq, block_size, num_heads, head_size);
-  const WorkspacePtrs ws = workspace_ptrs(workspace, w);
-  cudaStream_t cs = (cudaStream_t)stream;
-  // the tensor-core kernel takes M tiles packed across requests; APS_PACK_TILES=0 starts a new
-  // tile per request (what the CUDA-core kernel needs)
-  const char* pk = getenv("APS_PACK_TILES");
-  const bool pack_tiles = tensor_path && !(pk != nullptr && pk[0] == '0');
-  if ((st = launch_plan(ws, seq_lens, cache_type, block_tables, batch, max_blocks_per_seq, block_size, pack_tiles, cs)) != APS_OK) return st;
-  // K/V requests: on the call's stream before the re-projection kernel
-  if (key_cache != nullptr && value_cache != nullptr) {
-    if ((st = launch_kv_attention(ws, query, key_cache, value_cache, block_tables, seq_lens, s, cs)) != APS_OK) return st;
-  }
-  if (!tensor_path) {
-    SimtHiddenArgs sa{query, hidden_cache, w_k, b_k, w_v, b_v, block_tables, seq_lens,
-                      max_blocks_per_seq, block_size, num_heads, head_size, hidden_size,
-                      query_stride, hidden_row_stride, w_stride, scale, dtype};
-    if ((st = launch_hidden_simt(ws, sa, cs)) != APS_OK) return st;
-    return launch_combine(ws, out, seq_lens, s, cs);
-  }
-  HiddenParams p{};
-  p.plan = ws.plan; p.part_offset = ws.part_offset; p.hid_subs = ws.hid_subs; p.first_tile = ws.first_tile; p.hid_rows = ws.hid_rows;
-  p.part_ml = ws.part_ml; p.part_acc = ws.part_acc; p.query = query;
-  p.block_tables = block_tables; p.seq_lens = seq_lens;
-  p.max_blocks_per_seq = max_blocks_per_seq; p.block_size = block_size;
-  p.query_stride = query_stride; p.scale_log2 = scale * 1.4426950408889634f;
-  p.b_k = b_k; p.b_v = b_v; p.heads = num_heads; p.k_slabs = (hidden_size + 63) / 64;
-  p.status = ws.plan + kPlanStatus;
-  p.stats = getenv("APS_STATS") != nullptr ? reinterpret_cast<unsigned long long*>(ws.plan + kPlanStatsWord) : nullptr;
-  st = dtype == APS_BF16 ? launch_hidden<__nv_bfloat16, kModeAttend>(mx, mk, mv, p, cs)
-                         : launch_hidden<__half, kModeAttend>(mx, mk, mv, p, cs);
-  if (st != APS_OK) return st;
-  return launch_combine(ws, out, seq_lens, s, cs);
+  return enqueue_hybrid_attention(c, (cudaStream_t)stream);
 }
 
 extern "C" int aps_kv_reprojection(void* kv, const void* x, const int32_t* block_ids, int64_t n_rows,
@@ -1130,8 +994,7 @@ extern "C" int aps_kv_reprojection(void* kv, const void* x, const int32_t* block
               APS_ERR_MISALIGNED, "kv_reprojection: output must be 16-byte aligned with a 16-byte row stride");
   APS_REQUIRE((n_rows + kBM - 1) / kBM < (1LL << 24), APS_ERR_SHAPE, "kv_reprojection: too many rows");
   CUtensorMap mx, mk, mv;
-  const char* dense_env = getenv("APS_DENSE_A");
-  const bool dense = block_ids == nullptr && !(dense_env != nullptr && dense_env[0] == '0');
+  const bool dense = block_ids == nullptr;   // contiguous X rows: one 128-row box per tile
   if ((st = make_maps(a, &mx, &mk, &mv, dense)) != APS_OK) return st;
   HiddenParams p{};
   p.dense_a = dense ? 1 : 0;
@@ -1142,4 +1005,25 @@ extern "C" int aps_kv_reprojection(void* kv, const void* x, const int32_t* block
   cudaStream_t cs = (cudaStream_t)stream;
   return dtype == APS_BF16 ? launch_hidden<__nv_bfloat16, kModeStore>(mx, mk, mv, p, cs)
                            : launch_hidden<__half, kModeStore>(mx, mk, mv, p, cs);
+}
+
+extern "C" int aps_selftest_bounded_wait(void* workspace, size_t workspace_bytes, long long budget_cycles,
+                                         void* out, int batch, int max_blocks_per_seq, int num_heads,
+                                         int head_size, int block_size, int64_t out_stride, int dtype,
+                                         void* stream) {
+  APS_REQUIRE(workspace != nullptr && out != nullptr, APS_ERR_NULL_POINTER, "selftest_bounded_wait: null pointer");
+  APS_REQUIRE(budget_cycles > 0 && budget_cycles <= 100000000LL, APS_ERR_SHAPE,
+              "selftest_bounded_wait: the budget must be between 1 and 1e8 clock cycles");
+  APS_REQUIRE(batch > 0 && max_blocks_per_seq > 0 && num_heads > 0 && head_size > 0 && block_size > 0,
+              APS_ERR_SHAPE, "selftest_bounded_wait: bad sizes");
+  const WorkspaceLayout w = workspace_layout(batch, max_blocks_per_seq, block_size, num_heads, head_size);
+  APS_REQUIRE(aligned_to(workspace, 256) && workspace_bytes >= w.total, APS_ERR_WORKSPACE,
+              "selftest_bounded_wait: workspace too small for this shape");
+  const WorkspacePtrs ws = workspace_ptrs(workspace, w);
+  cudaStream_t cs = (cudaStream_t)stream;
+  bounded_wait_selftest_kernel<<<1, 32, 0, cs>>>(ws.plan + kPlanStatus, budget_cycles, kStatusWaitLast);
+  int st = launch_status("bounded_wait_selftest_kernel");
+  if (st != APS_OK) return st;
+  AttnShape s{batch, max_blocks_per_seq, num_heads, head_size, block_size, 0, out_stride, 0, 1.f, dtype};
+  return launch_combine(ws, out, nullptr, s, cs);
 }

@@ -12,6 +12,12 @@
 //                   among the K/V-cached / hidden-cached requests;
 //   fill_kernel     one CTA per request: writes the request's entries of all eight tensors.
 // Integer work only; results are bit-identical to the host construction.
+//
+// The caller sizes the outputs from its own view of the batch (num_tot_tokens,
+// num_hidden_tokens) and may pass NULL for an output that is empty in that view.  The kernels
+// trust neither: layout_kernel recomputes the four totals from the device-side seq_lens and
+// cache_type, and fill_kernel writes nothing at all unless they equal the caller's claim;
+// every store is bounded by its tensor's capacity besides.
 
 #include "aps_common.cuh"
 
@@ -20,11 +26,11 @@ namespace {
 
 constexpr int kScanThreads = 1024;
 
-struct MetaLayout {       // per request, in the caller's scratch
+struct MetaLayout {       // per request, in the caller's scratch; entry [B] of each = the total
   int* exp_off;           // [B + 1] start in the expanded token space
   int* hid_off;           // [B + 1] start among the hidden tokens
-  int* kv_ord;            // [B]     ordinal among the K/V-cached requests
-  int* hid_ord;           // [B]     ordinal among the hidden-cached requests
+  int* kv_ord;            // [B + 1] ordinal among the K/V-cached requests
+  int* hid_ord;           // [B + 1] ordinal among the hidden-cached requests
 };
 
 __global__ void __launch_bounds__(kScanThreads)
@@ -59,6 +65,7 @@ layout_kernel(MetaLayout L, const int32_t* __restrict__ seq_lens, const int32_t*
   }
   if (tid == kScanThreads - 1) {
     L.exp_off[batch] = s[0][tid]; L.hid_off[batch] = s[1][tid];
+    L.kv_ord[batch] = s[2][tid]; L.hid_ord[batch] = s[3][tid];
     if (counts != nullptr) { counts[0] = s[0][tid]; counts[1] = s[1][tid]; counts[2] = s[2][tid]; counts[3] = s[3][tid]; }
   }
 }
@@ -67,13 +74,18 @@ struct MetaOut {
   int64_t* slot_mapping; int64_t* slot_mapping_shared; int64_t* hidden_cache_use_tot;
   int64_t* kv_cache_use_tot; int64_t* hidden_holder_upd; int64_t* hidden_holder_pull;
   int64_t* hidden_cache_store_tot; int64_t* hidden_cache_use_input;
-  int64_t cap_tot, cap_hidden;   // capacities of the [N_tot] and [N_h] tensors
+  int64_t cap_tot, cap_hidden;   // capacities of the [N_tot] and [N_h] tensors (the caller's claim)
+  int64_t cap_kv_req, cap_hid_req;   // capacities of the per-request lists [n_kv] and [n_h]
 };
 
 __global__ void __launch_bounds__(256)
 fill_kernel(MetaLayout L, MetaOut O, const int32_t* __restrict__ block_tables,
             const int32_t* __restrict__ block_tables_shared, const int32_t* __restrict__ seq_lens,
             const int32_t* __restrict__ cache_type, int batch, int max_blocks, int block_size) {
+  // the device-side totals must be what the caller sized (and NULL-ed) the outputs for
+  if (L.exp_off[batch] != O.cap_tot || L.hid_off[batch] != O.cap_hidden ||
+      L.kv_ord[batch] != O.cap_kv_req || L.hid_ord[batch] != O.cap_hid_req)
+    return;
   for (int r = blockIdx.x; r < batch; r += gridDim.x) {
     const int len = max(1, min(seq_lens[r], max_blocks * block_size));
     const int64_t e0 = L.exp_off[r];
@@ -93,13 +105,16 @@ fill_kernel(MetaLayout L, MetaOut O, const int32_t* __restrict__ block_tables,
       }
       if (threadIdx.x == 0) {
         O.hidden_holder_upd[r] = e0 + len - 1;
-        O.hidden_cache_store_tot[L.hid_ord[r]] = e0 + len - 1;
-        O.hidden_cache_use_input[L.hid_ord[r]] = r;
+        const int ord = L.hid_ord[r];
+        if (ord < O.cap_hid_req) {
+          O.hidden_cache_store_tot[ord] = e0 + len - 1;
+          O.hidden_cache_use_input[ord] = r;
+        }
       }
     } else if (threadIdx.x == 0) {
       const int j = len - 1;
       if (e0 < O.cap_tot) O.slot_mapping[e0] = (int64_t)priv[j / block_size] * block_size + j % block_size;
-      O.kv_cache_use_tot[L.kv_ord[r]] = e0;
+      if (L.kv_ord[r] < O.cap_kv_req) O.kv_cache_use_tot[L.kv_ord[r]] = e0;
       O.hidden_holder_upd[r] = e0;
     }
   }
@@ -124,12 +139,15 @@ extern "C" int aps_expand_decode_metadata(const int32_t* block_tables, const int
                                           int64_t num_hidden_tokens, int64_t* counts, void* scratch,
                                           size_t scratch_bytes, void* stream) {
   APS_REQUIRE(batch >= 0 && max_blocks_per_seq > 0 && block_size > 0 && num_tot_tokens >= batch &&
-                  num_hidden_tokens >= 0,
-              APS_ERR_SHAPE, "expand_decode_metadata: bad sizes");
+                  num_hidden_tokens >= 0 && num_hidden_tokens <= num_tot_tokens &&
+                  num_tot_tokens - num_hidden_tokens <= batch,
+              APS_ERR_SHAPE, "expand_decode_metadata: bad sizes (N_tot = %lld, N_h = %lld, batch = %d)",
+              (long long)num_tot_tokens, (long long)num_hidden_tokens, batch);
   if (batch == 0) return APS_OK;
   // outputs whose length is zero for this batch may be NULL (an empty tensor has no storage)
   APS_REQUIRE(block_tables && seq_lens && cache_type && slot_mapping && hidden_holder_upd,
               APS_ERR_NULL_POINTER, "expand_decode_metadata: null pointer");
+  // every hidden request holds at least one token, so N_h == 0 means there is none
   APS_REQUIRE(num_hidden_tokens == 0 || (block_tables_shared && slot_mapping_shared &&
                                          hidden_cache_use_tot && hidden_cache_store_tot &&
                                          hidden_cache_use_input),
@@ -146,7 +164,8 @@ extern "C" int aps_expand_decode_metadata(const int32_t* block_tables, const int
   MetaLayout L{sc, sc + (batch + 1), sc + 2 * (batch + 1), sc + 3 * (batch + 1)};
   MetaOut O{slot_mapping, slot_mapping_shared, hidden_cache_use_tot, kv_cache_use_tot,
             hidden_holder_upd, hidden_holder_pull, hidden_cache_store_tot, hidden_cache_use_input,
-            num_tot_tokens, num_hidden_tokens};
+            num_tot_tokens, num_hidden_tokens, num_tot_tokens - num_hidden_tokens,
+            batch - (num_tot_tokens - num_hidden_tokens)};
   cudaStream_t cs = (cudaStream_t)stream;
   layout_kernel<<<1, kScanThreads, 0, cs>>>(L, seq_lens, cache_type, batch,
                                             max_blocks_per_seq * block_size, counts);

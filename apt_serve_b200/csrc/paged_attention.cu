@@ -5,14 +5,24 @@
 // one query token per request over caches laid out [NB, BS, H, D]
 // (additional_designs/worker/aptserve_cache_engine.py:61-80).
 //
-// Work unit: one warp streams one head of one 128-token chunk.  A K (or V) row
-// of one head is D*sizeof(T) contiguous bytes; LPR = that / 16 lanes cover a row
-// with one 16-byte load each, so a warp-wide load fetches 32/LPR whole rows.
-// Scores are reduced over the LPR lanes with shuffles; the softmax is the
-// online (running max / running sum) form in the log2 domain.  Loads for the
-// next group of tokens are issued before the arithmetic of the current one, so
-// every thread keeps 8..16 independent 16-byte loads in flight.
-// CTAs are persistent and take 8 warp-units at a time from an atomic counter.
+// Work unit: one warp streams one head of one 128-token chunk, 16 tokens at a time,
+// every lane with 8 independent 16-byte loads of K and 8 of V in flight; the softmax is
+// the online (running max / running sum) form in the log2 domain.  Two kernels:
+//
+//   kv_attention_mma_kernel  (fp16 / bf16, head sizes 64 / 128)  The kernel is
+//       HBM-bound only while the SMs can issue the arithmetic that goes with every byte,
+//       and inside a decode step it runs at the ~1 GHz the board's power cap leaves next to
+//       the re-projection kernel.  So the two small products go to the tensor cores as
+//       mma.sync m16n8k16 with the single query row in row 0 of the A operand: the 16-byte
+//       vectors a lane loads ARE its B fragments (K: two MMAs per vector, no conversion, no
+//       shuffle reduction; V: token pairs are packed with one byte-permute per fragment
+//       register), the score fragment of Q K^T is, rounded to the cache's type, the A
+//       fragment of P V, and the accumulators stay fp32.  About 170 instructions per 16
+//       tokens and warp instead of about 800 on the CUDA cores.
+//   kv_attention_kernel      (fp32; head sizes 32 and 256)  CUDA-core arithmetic: LPR = row
+//       bytes / 16 lanes cover a row with one 16-byte load each, scores are reduced over
+//       those lanes with shuffles.
+// CTAs are persistent; work is handed out through an atomic counter.
 
 #include "attention_common.cuh"
 
@@ -45,13 +55,18 @@ plan_kernel(int* __restrict__ plan, int* __restrict__ part_offset, int2* __restr
             int2* __restrict__ hid_tiles, int* __restrict__ first_tile, int2* __restrict__ hid_subs,
             int* __restrict__ hid_rows, const int32_t* __restrict__ seq_lens,
             const int32_t* __restrict__ cache_type, const int32_t* __restrict__ block_tables, int batch,
-            int max_tokens, int max_blocks, int block_size, int pack_tiles) {
+            int max_tokens, int max_blocks, int block_size, int pack_tiles, int kv_present) {
   __shared__ int sa[kPlanThreads], sb[kPlanThreads];
+  __shared__ int s_kv_missing;
   const int tid = threadIdx.x;
+  if (tid == 0) s_kv_missing = 0;
+  __syncthreads();
   const int per = (batch + kPlanThreads - 1) / kPlanThreads;
   const int r0 = min(batch, tid * per), r1 = min(batch, r0 + per);
   auto seq_of = [&](int r) { return max(0, min(seq_lens[r], max_tokens)); };
   auto hidden = [&](int r) { return cache_type != nullptr && cache_type[r] != 0; };
+  // without a K/V cache a K/V-cached request gets no chunks and no partials: its output row is zero
+  auto chunks_of = [&](int s) { return kv_present ? (s + kChunkTokens - 1) / kChunkTokens : 0; };
   auto subs_of = [&](int s) {   // sub-blocks a hidden request of s tokens occupies in the tile list
     const int n = (s + kSubRowsPlan - 1) / kSubRowsPlan;
     return pack_tiles ? n : (n + 7) / 8 * 8;
@@ -60,7 +75,8 @@ plan_kernel(int* __restrict__ plan, int* __restrict__ part_offset, int2* __restr
   int kv = 0, sub = 0;
   for (int r = r0; r < r1; ++r) {
     const int s = seq_of(r);
-    if (hidden(r)) sub += subs_of(s); else kv += (s + kChunkTokens - 1) / kChunkTokens;
+    if (hidden(r)) sub += subs_of(s);
+    else { kv += chunks_of(s); if (!kv_present) s_kv_missing = 1; }
   }
   int kv_inc = kv, sub_inc = sub;
   block_scan2(sa, sb, tid, kv_inc, sub_inc);
@@ -78,7 +94,7 @@ plan_kernel(int* __restrict__ plan, int* __restrict__ part_offset, int2* __restr
         if (real > 0) slots += (g + real - 1) / 8 - g / 8 + 1;
         g += n;
       } else {
-        slots += (s + kChunkTokens - 1) / kChunkTokens;
+        slots += chunks_of(s);
       }
     }
   }
@@ -108,7 +124,7 @@ plan_kernel(int* __restrict__ plan, int* __restrict__ part_offset, int2* __restr
         g += n;
       } else {
         first_tile[r] = 0;
-        const int c = (s + kChunkTokens - 1) / kChunkTokens;
+        const int c = chunks_of(s);
         q_at[tid] = o_kv; q_n[tid] = c; q_real[tid] = -1;   // -1 marks a K/V request
         o_kv += c;
         o_slot += c;
@@ -151,7 +167,7 @@ plan_kernel(int* __restrict__ plan, int* __restrict__ part_offset, int2* __restr
     plan[kPlanNumHidSubs] = total_sub;
     plan[kPlanKvCounter] = 0;
     plan[kPlanHidCounter] = 0;
-    plan[kPlanStatus] = 0;
+    plan[kPlanStatus] = s_kv_missing ? kStatusNoKvCache : kStatusOk;
     // entries between the last sub-block and the end of the last tile read as padding
     for (int j = total_sub; j < (total_sub + 7) / 8 * 8; ++j) hid_subs[j] = make_int2(-1, 0);
   }
@@ -291,11 +307,218 @@ kv_attention_kernel(int* __restrict__ plan, const int* __restrict__ part_offset,
   }
 }
 
+// ---- K/V streaming, products on the tensor cores -------------------------------------
+// mma.sync.m16n8k16 fragments (g = lane / 4, j = lane % 4):
+//   A (16 x 16, row major)  a0 = (row g, k = 2j, 2j+1)   a2 = (row g, k = 2j+8, 2j+9)
+//                           a1, a3 = the same for row g + 8
+//   B (16 x 8, column major) b0 = (k = 2j, 2j+1, column g)  b1 = (k = 2j+8, 2j+9, column g)
+//   C (16 x 8, fp32)         c0, c1 = (row g, columns 2j, 2j+1)   c2, c3 = row g + 8
+// Only row 0 of A holds data (the one query row), so only lanes 0..3 hold results.
+template <typename T> struct Mma16816;
+template <> struct Mma16816<__half> {
+  // d0, d1 accumulate in place; rows 8..15 (a1, a3, c2, c3) are zero on input and dropped on output
+  static __device__ __forceinline__ void run(float& d0, float& d1, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    float x2, x3;
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %5}, {%7, %8}, {%0, %1, %9, %9};"
+                 : "+f"(d0), "+f"(d1), "=f"(x2), "=f"(x3)
+                 : "r"(a0), "r"(0u), "r"(a2), "r"(b0), "r"(b1), "f"(0.f));
+  }
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
+};
+template <> struct Mma16816<__nv_bfloat16> {
+  static __device__ __forceinline__ void run(float& d0, float& d1, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    float x2, x3;
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %5}, {%7, %8}, {%0, %1, %9, %9};"
+                 : "+f"(d0), "+f"(d1), "=f"(x2), "=f"(x3)
+                 : "r"(a0), "r"(0u), "r"(a2), "r"(b0), "r"(b1), "f"(0.f));
+  }
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
+};
+
+__device__ __forceinline__ uint32_t word_of(const uint4& v, int i) {
+  return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w;
+}
+
+constexpr int kMmaWarps = 4;       // warps per CTA of the tensor-core streaming kernel
+constexpr int kMmaCtasPerSm = 3;
+constexpr int kGroupTokens = 16;   // tokens per softmax step
+
+// K of a 16-token group: two 8-token blocks; lane (g, j) loads, for token g of each block, the
+// 16-byte pieces [c*32 + j*8, +8) of the head's row, c < D/32: four lanes cover 64 contiguous
+// bytes, a warp-wide load 8 rows.  Piece c is the B fragment pair of MMAs (c, 0) = words x, y and
+// (c, 1) = words z, w; the query piece at the same offset gives the matching A fragments.
+// V of the group: lane (g, j) loads, for tokens 2j, 2j+1, 2j+8, 2j+9, the pieces
+// [q*64 + g*8, +8), q < D/64: eight lanes cover 128 contiguous bytes of a row.  Element e of the
+// piece, taken from the four tokens, is the B fragment of MMA (q, e), whose output column of
+// lane j is head element q*64 + 16j + e (c0) and q*64 + 16j + 8 + e (c1).
+template <typename T, int D>
+__global__ void __launch_bounds__(kMmaWarps * 32, kMmaCtasPerSm)
+kv_attention_mma_kernel(int* __restrict__ plan, const int* __restrict__ part_offset,
+                        const int2* __restrict__ kv_chunks, float* __restrict__ part_ml,
+                        float* __restrict__ part_acc, const T* __restrict__ query,
+                        const T* __restrict__ key_cache, const T* __restrict__ value_cache,
+                        const int32_t* __restrict__ block_tables, const int32_t* __restrict__ seq_lens,
+                        int max_blocks_per_seq, int heads, int block_size, int64_t query_stride,
+                        int64_t block_stride, float scale_log2) {
+  static_assert(sizeof(T) == 2 && (D == 64 || D == 128), "tensor-core streaming kernel: 2-byte types, head size 64 or 128");
+  constexpr int NC = D / 32;   // 16-byte K pieces per lane and token
+  constexpr int NQ = D / 64;   // 16-byte V pieces per lane and token
+  using M = Mma16816<T>;
+  const int lane = threadIdx.x & 31;
+  const int g = lane >> 2, j = lane & 3;
+  const int total = plan[kPlanNumKvChunks] * heads;
+  const int64_t row_stride = (int64_t)heads * D;
+
+  int unit = 0;
+  if (lane == 0) unit = atomicAdd(&plan[kPlanKvCounter], 1);
+  unit = __shfl_sync(kFull, unit, 0);
+  while (unit < total) {
+    // the next unit's index is fetched while this one is streamed
+    int next_unit = 0;
+    if (lane == 0) next_unit = atomicAdd(&plan[kPlanKvCounter], 1);
+
+    const int2 rc = kv_chunks[unit / heads];
+    const int h = unit % heads;
+    const int req = rc.x;
+    const int seq = min(seq_lens[req], max_blocks_per_seq * block_size);
+    const int tok_begin = rc.y * kChunkTokens;
+    const int tok_end = min(seq, tok_begin + kChunkTokens);
+    const int n_groups = (tok_end - tok_begin + kGroupTokens - 1) / kGroupTokens;
+    // block-table entry of each of the chunk's groups (a group never straddles a cache block:
+    // block sizes are multiples of 16), one per lane, handed out by shuffle
+    int my_blk = 0;
+    if (lane < n_groups)
+      my_blk = block_tables[(int64_t)req * max_blocks_per_seq + (tok_begin + lane * kGroupTokens) / block_size];
+
+    // A fragments of the query row (lanes 0..3 = row 0; the other rows are zero)
+    uint32_t qa[NC][4];
+#pragma unroll
+    for (int c = 0; c < NC; ++c) {
+      uint4 qv = make_uint4(0, 0, 0, 0);
+      if (g == 0) qv = *reinterpret_cast<const uint4*>(query + req * query_stride + h * D + c * 32 + j * 8);
+      qa[c][0] = qv.x; qa[c][1] = qv.y; qa[c][2] = qv.z; qa[c][3] = qv.w;
+    }
+    float acc[NQ][8][2];
+#pragma unroll
+    for (int q = 0; q < NQ; ++q)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[q][e][0] = acc[q][e][1] = 0.f;
+    float m = -INFINITY, l = 0.f;
+
+    const T* k_head = key_cache + h * D + j * 8;     // + block and row offsets
+    const T* v_head = value_cache + h * D + g * 8;
+    uint4 kreg[2][NC], vreg[4][NQ];
+    auto load_k = [&](int gi) {
+      const int blk = __shfl_sync(kFull, my_blk, gi);
+      const int tb = tok_begin + gi * kGroupTokens;
+      const T* base = k_head + (int64_t)blk * block_stride + (int64_t)(tb % block_size + g) * row_stride;
+#pragma unroll
+      for (int b = 0; b < 2; ++b) {
+        const bool live = tb + b * 8 + g < tok_end;
+#pragma unroll
+        for (int c = 0; c < NC; ++c)
+          kreg[b][c] = live ? ld_stream16(base + (int64_t)b * 8 * row_stride + c * 32) : make_uint4(0, 0, 0, 0);
+      }
+    };
+    auto load_v = [&](int gi) {
+      const int blk = __shfl_sync(kFull, my_blk, gi);
+      const int tb = tok_begin + gi * kGroupTokens;
+      const T* base = v_head + (int64_t)blk * block_stride + (int64_t)(tb % block_size + 2 * j) * row_stride;
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const int off = (t & 1) + (t >> 1) * 8;            // tokens 2j, 2j+1, 2j+8, 2j+9 of the group
+        const bool live = tb + 2 * j + off < tok_end;
+#pragma unroll
+        for (int q = 0; q < NQ; ++q)
+          vreg[t][q] = live ? ld_stream16(base + (int64_t)off * row_stride + q * 64) : make_uint4(0, 0, 0, 0);
+      }
+    };
+
+    load_k(0);
+    for (int gi = 0; gi < n_groups; ++gi) {
+      load_v(gi);
+      // ---- scores of the group's two 8-token blocks: row 0 of Q K^T ----
+      float sc[2][2][2];   // [block][partial chain][column]
+#pragma unroll
+      for (int b = 0; b < 2; ++b) {
+        sc[b][0][0] = sc[b][0][1] = sc[b][1][0] = sc[b][1][1] = 0.f;
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {
+          M::run(sc[b][0][0], sc[b][0][1], qa[c][0], qa[c][1], kreg[b][c].x, kreg[b][c].y);
+          M::run(sc[b][1][0], sc[b][1][1], qa[c][2], qa[c][3], kreg[b][c].z, kreg[b][c].w);
+        }
+      }
+      if (gi + 1 < n_groups) load_k(gi + 1);
+      // ---- online softmax over the 16 tokens (lane j of row 0: tokens 2j, 2j+1 of each block) ----
+      const int tb = tok_begin + gi * kGroupTokens;
+      float s[2][2];
+      float gm = -INFINITY;
+#pragma unroll
+      for (int b = 0; b < 2; ++b)
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const float v = (sc[b][0][i] + sc[b][1][i]) * scale_log2;
+          s[b][i] = tb + b * 8 + 2 * j + i < tok_end ? v : -INFINITY;
+          gm = fmaxf(gm, s[b][i]);
+        }
+      gm = fmaxf(gm, __shfl_xor_sync(kFull, gm, 1));
+      gm = fmaxf(gm, __shfl_xor_sync(kFull, gm, 2));
+      const float m_new = fmaxf(m, gm);   // finite: every group holds at least one valid token
+      const float corr = exp2f(m - m_new);
+      m = m_new;
+      float p[2][2];
+#pragma unroll
+      for (int b = 0; b < 2; ++b)
+#pragma unroll
+        for (int i = 0; i < 2; ++i) p[b][i] = exp2f(s[b][i] - m_new);
+      l = l * corr + (p[0][0] + p[0][1]) + (p[1][0] + p[1][1]);
+      // the score fragment, rounded to the cache's type, is the A fragment of P V
+      const uint32_t pa0 = M::pack(p[0][0], p[0][1]), pa2 = M::pack(p[1][0], p[1][1]);
+      // ---- weighted V rows: row 0 of P V ----
+#pragma unroll
+      for (int q = 0; q < NQ; ++q)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const uint32_t sel = (e & 1) ? 0x7632u : 0x5410u;
+          const uint32_t b0 = __byte_perm(word_of(vreg[0][q], e >> 1), word_of(vreg[1][q], e >> 1), sel);
+          const uint32_t b1 = __byte_perm(word_of(vreg[2][q], e >> 1), word_of(vreg[3][q], e >> 1), sel);
+          acc[q][e][0] *= corr; acc[q][e][1] *= corr;
+          M::run(acc[q][e][0], acc[q][e][1], pa0, pa2, b0, b1);
+        }
+    }
+    // ---- the partial: lanes 0..3 hold row 0 ----
+    l += __shfl_xor_sync(kFull, l, 1);
+    l += __shfl_xor_sync(kFull, l, 2);
+    if (g == 0) {
+      const int64_t slot = (int64_t)(part_offset[req] + rc.y) * heads + h;
+#pragma unroll
+      for (int q = 0; q < NQ; ++q) {
+        float* dst = part_acc + slot * D + q * 64 + 16 * j;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          *reinterpret_cast<float4*>(dst + 8 * i) = make_float4(acc[q][0][i], acc[q][1][i], acc[q][2][i], acc[q][3][i]);
+          *reinterpret_cast<float4*>(dst + 8 * i + 4) = make_float4(acc[q][4][i], acc[q][5][i], acc[q][6][i], acc[q][7][i]);
+        }
+      }
+      if (lane == 0) *reinterpret_cast<float2*>(part_ml + slot * 2) = make_float2(m, l);
+    }
+    unit = __shfl_sync(kFull, next_unit, 0);
+  }
+}
+
 // ---- combine -------------------------------------------------------------------
-// One warp per (request, head): merge the request's partials in chunk order.
+// One warp per (request, head): merge the request's partials in chunk order.  When a bounded
+// wait of the re-projection kernel ran out (status word 1..7) some partials were never
+// written: the whole output is filled with NaN instead of numbers that look plausible.
 template <typename T>
 __global__ void __launch_bounds__(256)
-combine_kernel(const int* __restrict__ part_offset, const float* __restrict__ part_ml,
+combine_kernel(const int* __restrict__ plan, const int* __restrict__ part_offset, const float* __restrict__ part_ml,
                const float* __restrict__ part_acc, T* __restrict__ out, int batch, int heads,
                int head_size, int64_t out_stride) {
   const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -303,6 +526,12 @@ combine_kernel(const int* __restrict__ part_offset, const float* __restrict__ pa
   if (unit >= batch * heads) return;
   const int req = unit / heads, h = unit % heads;
   const int p0 = part_offset[req], p1 = part_offset[req + 1];
+  T* dst = out + req * out_stride + (int64_t)h * head_size;
+  const int status = plan[kPlanStatus];
+  if (status >= kStatusWaitFirst && status <= kStatusWaitLast) {
+    for (int d = lane; d < head_size; d += 32) dst[d] = Elem<T>::from_float(__int_as_float(0x7fc00000));
+    return;
+  }
   float mx = -INFINITY;
   for (int p = p0; p < p1; ++p) mx = fmaxf(mx, part_ml[((int64_t)p * heads + h) * 2]);
   float denom = 0.f;
@@ -311,7 +540,6 @@ combine_kernel(const int* __restrict__ part_offset, const float* __restrict__ pa
     denom += exp2f(ml.x - mx) * ml.y;
   }
   const float inv = (p1 > p0 && denom > 0.f) ? 1.f / denom : 0.f;
-  T* dst = out + req * out_stride + (int64_t)h * head_size;
   for (int d = lane; d < head_size; d += 32) {
     float a = 0.f;
     for (int p = p0; p < p1; ++p) {
@@ -326,11 +554,19 @@ template <typename T, int D>
 int launch_kv_typed(const WorkspacePtrs& ws, const void* query, const void* key_cache,
                     const void* value_cache, const int32_t* block_tables, const int32_t* seq_lens,
                     const AttnShape& s, cudaStream_t stream) {
-  // 2 persistent CTAs of 8 warps per SM
-  const int grid = sm_count() * 2;
-  const int threads = kKvWarps * 32;
   const float scale_log2 = s.scale * 1.4426950408889634f;
   ScopedProfile prof(0, stream);
+  if constexpr (sizeof(T) == 2 && (D == 64 || D == 128)) {
+    // tensor-core arithmetic: 3 persistent CTAs of 4 warps per SM
+    kv_attention_mma_kernel<T, D><<<sm_count() * kMmaCtasPerSm, kMmaWarps * 32, 0, stream>>>(
+        ws.plan, ws.part_offset, ws.kv_chunks, ws.part_ml, ws.part_acc, (const T*)query,
+        (const T*)key_cache, (const T*)value_cache, block_tables, seq_lens, s.max_blocks_per_seq,
+        s.heads, s.block_size, s.query_stride, s.block_stride, scale_log2);
+    return launch_status("kv_attention_mma_kernel");
+  }
+  // CUDA-core arithmetic: 2 persistent CTAs of 8 warps per SM
+  const int grid = sm_count() * 2;
+  const int threads = kKvWarps * 32;
   kv_attention_kernel<T, D><<<grid, threads, 0, stream>>>(
       ws.plan, ws.part_offset, ws.kv_chunks, ws.part_ml, ws.part_acc, (const T*)query,
       (const T*)key_cache, (const T*)value_cache, block_tables, seq_lens, s.max_blocks_per_seq,
@@ -363,12 +599,12 @@ bool kv_attention_supported(int dtype, int head_size) {
 
 int launch_plan(const WorkspacePtrs& ws, const int32_t* seq_lens, const int32_t* cache_type,
                 const int32_t* block_tables, int batch, int max_blocks_per_seq, int block_size,
-                bool pack_tiles, cudaStream_t stream) {
+                bool pack_tiles, bool kv_present, cudaStream_t stream) {
   plan_kernel<<<1, kPlanThreads, 0, stream>>>(ws.plan, ws.part_offset, ws.kv_chunks, ws.hid_tiles,
                                               ws.first_tile, ws.hid_subs, ws.hid_rows, seq_lens,
                                               cache_type, block_tables, batch,
                                               max_blocks_per_seq * block_size, max_blocks_per_seq,
-                                              block_size, pack_tiles ? 1 : 0);
+                                              block_size, pack_tiles ? 1 : 0, kv_present ? 1 : 0);
   return launch_status("plan_kernel");
 }
 
@@ -390,15 +626,15 @@ int launch_combine(const WorkspacePtrs& ws, void* out, const int32_t* seq_lens, 
   const int grid = (units + 7) / 8;
   switch (s.dtype) {
     case APS_F32:
-      combine_kernel<float><<<grid, 256, 0, stream>>>(ws.part_offset, ws.part_ml, ws.part_acc,
+      combine_kernel<float><<<grid, 256, 0, stream>>>(ws.plan, ws.part_offset, ws.part_ml, ws.part_acc,
                                                      (float*)out, s.batch, s.heads, s.head_size, s.out_stride);
       break;
     case APS_F16:
-      combine_kernel<__half><<<grid, 256, 0, stream>>>(ws.part_offset, ws.part_ml, ws.part_acc,
+      combine_kernel<__half><<<grid, 256, 0, stream>>>(ws.plan, ws.part_offset, ws.part_ml, ws.part_acc,
                                                       (__half*)out, s.batch, s.heads, s.head_size, s.out_stride);
       break;
     case APS_BF16:
-      combine_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(ws.part_offset, ws.part_ml, ws.part_acc,
+      combine_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(ws.plan, ws.part_offset, ws.part_ml, ws.part_acc,
                                                              (__nv_bfloat16*)out, s.batch, s.heads, s.head_size, s.out_stride);
       break;
     default: return fail(APS_ERR_DTYPE, "decode attention: unsupported dtype %d", s.dtype);
@@ -464,7 +700,7 @@ extern "C" int aps_paged_decode_attention(void* out, const void* query, const vo
   const WorkspaceLayout w = workspace_layout(batch, max_blocks_per_seq, block_size, num_heads, head_size);
   const WorkspacePtrs ws = workspace_ptrs(workspace, w);
   cudaStream_t cs = (cudaStream_t)stream;
-  if ((st = launch_plan(ws, seq_lens, nullptr, block_tables, batch, max_blocks_per_seq, block_size, false, cs)) != APS_OK) return st;
+  if ((st = launch_plan(ws, seq_lens, nullptr, block_tables, batch, max_blocks_per_seq, block_size, false, true, cs)) != APS_OK) return st;
   if ((st = launch_kv_attention(ws, query, key_cache, value_cache, block_tables, seq_lens, s, cs)) != APS_OK) return st;
   return launch_combine(ws, out, seq_lens, s, cs);
 }
@@ -482,27 +718,22 @@ extern "C" int aps_attention_status(const void* workspace, int* host_status, voi
 // The scratch of aps_paged_decode_attention_static lives in this module's image: a
 // fixed array in device memory that every GPU which loads the library holds until the
 // process exits.  Host code may not pass the array's name to a kernel (on the host it
-// is only a handle); the device address is looked up once per device with
-// cudaGetSymbolAddress, with that device current, and cached.
+// is only a handle); the device address is looked up with cudaGetSymbolAddress, with the
+// calling thread's device current, on EVERY call: the lookup is a table read once the
+// module is loaded, and an address kept across calls would go stale when the host tears
+// its CUDA context down and creates a new one (cudaDeviceReset, a driver-API host).
 namespace aps {
 namespace {
 
 constexpr size_t kStaticScratchBytes = size_t(32) << 20;  // 32 MiB
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
-void* g_static_scratch_addr[64] = {nullptr};
 
 int static_scratch_address(void** out) {
-  int dev = 0;
-  APS_CUDA(cudaGetDevice(&dev));
-  APS_REQUIRE(dev >= 0 && dev < 64, APS_ERR_CUDA, "paged_decode_attention_static: device index %d out of range", dev);
-  if (g_static_scratch_addr[dev] == nullptr) {
-    void* p = nullptr;
-    APS_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
-    APS_REQUIRE(p != nullptr && aligned_to(p, 256), APS_ERR_CUDA,
-                "paged_decode_attention_static: built-in scratch has no usable device address");
-    g_static_scratch_addr[dev] = p;
-  }
-  *out = g_static_scratch_addr[dev];
+  void* p = nullptr;
+  APS_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+  APS_REQUIRE(p != nullptr && aligned_to(p, 256), APS_ERR_CUDA,
+              "paged_decode_attention_static: built-in scratch has no usable device address");
+  *out = p;
   return APS_OK;
 }
 
@@ -540,7 +771,7 @@ extern "C" int aps_paged_decode_attention_static(void* out, const void* query, c
   // plan_kernel rewrites every word of the scratch header (work counter, status word,
   // list sizes) and every partial that the combine reads is rewritten by this call, so
   // nothing left over from the previous call is ever read
-  if ((st = launch_plan(ws, seq_lens, nullptr, block_tables, batch, max_blocks_per_seq, block_size, false, cs)) != APS_OK) return st;
+  if ((st = launch_plan(ws, seq_lens, nullptr, block_tables, batch, max_blocks_per_seq, block_size, false, true, cs)) != APS_OK) return st;
   if ((st = launch_kv_attention(ws, query, key_cache, value_cache, block_tables, seq_lens, s, cs)) != APS_OK) return st;
   return launch_combine(ws, out, seq_lens, s, cs);
 }

@@ -31,6 +31,10 @@ def expand_decode_metadata(seq_lens: Sequence[int], use_hidden: Sequence[bool],
     dev = torch.device(device)
     b = len(seq_lens)
     lens = [int(s) for s in seq_lens]
+    if any(s < 1 for s in lens):
+        # the kernels count a length below 1 as 1; the host counts must agree with them
+        raise ValueError("expand_decode_metadata: every sequence length must be >= 1 "
+                         "(it includes the token being decoded)")
     hid = np.asarray(list(use_hidden), dtype=bool)
     n_tot = int(sum(s if h else 1 for s, h in zip(lens, hid)))
     n_hid_tok = int(sum(s for s, h in zip(lens, hid) if h))

@@ -16,7 +16,8 @@ import torch
 import torch.nn.functional as F
 
 from . import mixed_cache_ops, ops
-from .attention import Attention, hybrid_decode_attention, hybrid_decode_attention_absorbed
+from .attention import (Attention, absorbed_supported, decode_layer_step, hybrid_decode_attention,
+                        hybrid_decode_attention_absorbed)
 from .metadata import derive_private_block_tables
 
 
@@ -96,8 +97,9 @@ class OPTAttention(torch.nn.Module):
     for K/V requests, the new token's hidden row write for hidden requests, one
     hybrid decode attention call; a prefill batch with hidden-designated prompts
     writes both kinds of cache rows with one launch.  ``fused="absorbed"`` is the same with
-    the hidden requests attended through absorbed projections (fp16 / bf16).  ``fused=False`` runs the
-    reference's op sequence literally on this package's kernels.
+    the hidden requests attended through absorbed projections (fp16 / bf16; shapes the absorbed
+    kernels do not take -- see ``attention.absorbed_supported`` -- fall back to the re-projecting
+    kernel).  ``fused=False`` runs the reference's op sequence literally on this package's kernels.
 
     Under tensor parallelism ``hidden_cache`` must be given (a
     ``[2, NB, BS, 1, E]`` tensor replicated per rank); with one rank it defaults
@@ -139,11 +141,12 @@ class OPTAttention(torch.nn.Module):
             output, _ = self.out_proj(attn_output)
             return output
         if m.num_hidden_cache_tokens != 0:
+            if m.num_decode_tokens != 0 and self.fused:
+                # the new token's hidden rows are written by the fused step itself
+                return self._fused_decode(hidden_states, kv_cache, hcache, m)
             mixed_cache_ops.hidden_to_cache(hidden_states, hcache, m.slot_mapping,
                                             m.hidden_cache_use_input, m.hidden_cache_store_tot)
             if m.num_decode_tokens != 0:
-                if self.fused:
-                    return self._fused_decode(hidden_states, kv_cache, hcache, m)
                 holder = torch.zeros(m.num_tot_tokens, hidden_states.shape[1],
                                      device=hidden_states.device, dtype=hidden_states.dtype)
                 q, _ = self.qkv_proj(hidden_states, q_only=True)
@@ -162,6 +165,11 @@ class OPTAttention(torch.nn.Module):
         output, _ = self.out_proj(attn_output)
         return output
 
+    def use_absorbed(self, dtype: torch.dtype) -> bool:
+        """``fused="absorbed"`` takes the absorbed kernels only for the shapes they are
+        instantiated for; everything else runs the re-projecting kernel."""
+        return self.fused == "absorbed" and absorbed_supported(self.num_heads, self.embed_dim, dtype)
+
     def _fused_decode(self, hidden_states, kv_cache, hidden_cache, m) -> torch.Tensor:
         (w_q, b_q), (w_k, b_k), (w_v, b_v) = self.qkv_proj.slices()
         tables = getattr(m, "private_block_tables", None)
@@ -169,23 +177,30 @@ class OPTAttention(torch.nn.Module):
         if tables is None or ctype is None:
             tables, ctype = derive_private_block_tables(m, kv_cache.shape[2])
         q = F.linear(hidden_states, w_q, b_q)
+        k_new = v_new = None
         if m.kv_cache_use_tot.numel() != 0:
-            # new token of every K/V request: project and write to its private slot;
-            # rows of hidden requests get slot -1 and are skipped by the write
+            # new token of every K/V request: K/V projection of the step's rows (the rows of
+            # hidden requests are projected too and ignored by the write)
             hd = self.num_heads * self.head_dim
             kv = F.linear(hidden_states, self.qkv_proj.weight[hd:],
                           None if self.qkv_proj.bias is None else self.qkv_proj.bias[hd:])
-            slots = torch.where(ctype != 0, torch.full_like(m.hidden_holder_upd, -1),
-                                m.slot_mapping[m.hidden_holder_upd])
-            k_new = kv[:, :hd].view(-1, self.num_heads, self.head_dim)
-            v_new = kv[:, hd:].view(-1, self.num_heads, self.head_dim)
-            ops.reshape_and_cache_flash(k_new, v_new, kv_cache[0], kv_cache[1], slots, "auto")
-        if self.fused == "absorbed" and q.dtype in (torch.float16, torch.bfloat16):
+            k_new, v_new = kv[:, :hd], kv[:, hd:]
+        if self.use_absorbed(q.dtype):
+            mixed_cache_ops.hidden_to_cache(hidden_states, hidden_cache, m.slot_mapping,
+                                            m.hidden_cache_use_input, m.hidden_cache_store_tot)
+            if k_new is not None:
+                slots = torch.where(ctype != 0, torch.full_like(m.hidden_holder_upd, -1),
+                                    m.slot_mapping[m.hidden_holder_upd])
+                ops.reshape_and_cache_flash(k_new.view(-1, self.num_heads, self.head_dim),
+                                            v_new.view(-1, self.num_heads, self.head_dim),
+                                            kv_cache[0], kv_cache[1], slots, "auto")
             attn_output = hybrid_decode_attention_absorbed(
                 q, kv_cache, hidden_cache, w_k, b_k, w_v, b_v, tables, m.seq_lens_tensor, ctype,
                 self.scaling, hidden_rows=m.hidden_cache_use_input)
         else:
-            attn_output = hybrid_decode_attention(q, kv_cache, hidden_cache, w_k, b_k, w_v, b_v,
-                                                  tables, m.seq_lens_tensor, ctype, self.scaling)
+            # cache writes of the new tokens + attention in one native call
+            attn_output = decode_layer_step(q, hidden_states, k_new, v_new, kv_cache, hidden_cache,
+                                            w_k, b_k, w_v, b_v, tables, m.seq_lens_tensor, ctype,
+                                            self.scaling)
         output, _ = self.out_proj(attn_output)
         return output

@@ -4,7 +4,7 @@ calls (additional_designs/attention/backends/aptserve_flash_attn.py:44-65,
 from __future__ import annotations
 
 import ctypes
-from typing import List
+from typing import List, Optional
 
 import torch
 
@@ -35,33 +35,50 @@ def reshape_and_cache_flash(key: torch.Tensor, value: torch.Tensor, key_cache: t
             N.dtype_enum(key), N.current_stream(dev)))
 
 
-def prefill_cache_write(key: torch.Tensor, value: torch.Tensor, hidden_states: torch.Tensor,
-                        kv_cache: torch.Tensor, hidden_cache: torch.Tensor,
-                        slot_mapping: torch.Tensor, kv_cache_use_tot: torch.Tensor,
-                        hidden_cache_use_input: torch.Tensor) -> None:
+def prefill_cache_write(key: Optional[torch.Tensor], value: Optional[torch.Tensor],
+                        hidden_states: Optional[torch.Tensor], kv_cache: Optional[torch.Tensor],
+                        hidden_cache: Optional[torch.Tensor], slot_mapping: torch.Tensor,
+                        kv_cache_use_tot: Optional[torch.Tensor],
+                        hidden_cache_use_input: Optional[torch.Tensor]) -> None:
     """One launch for a prefill batch's cache writes: K/V rows of the K/V-designated
     prompt tokens (``kv_cache_use_tot``) into ``kv_cache``, layer-input rows of the
     hidden-designated ones (``hidden_cache_use_input``) into the flat rows of
     ``hidden_cache``; every token's slot is ``slot_mapping[token]``.  Stands in for
     ``hidden_to_cache`` + ``reshape_and_cache_flash(key[kv_cache_use_tot], ...)``
     (aptserve_opt.py:108-109, aptserve_flash_attn.py:347-355) without the gathered copies.
-    ``key`` / ``value``: ``[T, H, D]``; ``hidden_states``: ``[T, E]``."""
+    ``key`` / ``value``: ``[T, H, D]``; ``hidden_states``: ``[T, E]``.  Either half may be left
+    out (``None`` tensors and index list): only the other kind of row is written."""
     dev = N.require_cuda(key, value, hidden_states, kv_cache, hidden_cache, slot_mapping,
                          kv_cache_use_tot, hidden_cache_use_input)
+    has_kv = kv_cache_use_tot is not None and kv_cache_use_tot.numel() > 0
+    has_hid = hidden_cache_use_input is not None and hidden_cache_use_input.numel() > 0
+    if not has_kv and not has_hid:
+        return
+    if has_kv and (key is None or value is None or kv_cache is None):
+        raise RuntimeError("prefill_cache_write: K/V rows listed without key / value / kv_cache")
+    if has_hid and (hidden_states is None or hidden_cache is None):
+        raise RuntimeError("prefill_cache_write: hidden rows listed without hidden_states / hidden_cache")
     for t, name in ((slot_mapping, "slot_mapping"), (kv_cache_use_tot, "kv_cache_use_tot"),
                     (hidden_cache_use_input, "hidden_cache_use_input")):
-        if t.dtype != torch.int64:
+        if t is not None and t.dtype != torch.int64:
             raise RuntimeError(f"{name} must be int64")
-    if not (key.dtype == value.dtype == hidden_states.dtype == kv_cache.dtype == hidden_cache.dtype):
+    used = [t for t in ((key, value, kv_cache) if has_kv else ()) + ((hidden_states, hidden_cache) if has_hid else ())]
+    if any(t.dtype != used[0].dtype for t in used):
         raise RuntimeError("prefill_cache_write: dtypes differ")
+    heads, head_size, block_size = ((key.size(1), key.size(2), kv_cache.size(2)) if has_kv
+                                    else (1, 1, hidden_cache.size(2)))
     with torch.cuda.device(dev):
         N.check(N.lib().aps_prefill_cache_write(
-            N.ptr(key), N.ptr(value), N.ptr(hidden_states), N.ptr(kv_cache[0]), N.ptr(kv_cache[1]),
-            N.ptr(hidden_cache), N.ptr(slot_mapping.contiguous()), N.ptr(kv_cache_use_tot.contiguous()),
-            kv_cache_use_tot.numel(), N.ptr(hidden_cache_use_input.contiguous()),
-            hidden_cache_use_input.numel(), key.size(1), key.size(2), hidden_states.size(1),
-            kv_cache.size(2), key.stride(0), value.stride(0), hidden_states.stride(0),
-            kv_cache.stride(1), hidden_cache.stride(2), N.dtype_enum(key), N.current_stream(dev)))
+            N.ptr(key) if has_kv else 0, N.ptr(value) if has_kv else 0, N.ptr(hidden_states) if has_hid else 0,
+            N.ptr(kv_cache[0]) if has_kv else 0, N.ptr(kv_cache[1]) if has_kv else 0,
+            N.ptr(hidden_cache) if has_hid else 0, N.ptr(slot_mapping.contiguous()),
+            N.ptr(kv_cache_use_tot.contiguous()) if has_kv else 0, kv_cache_use_tot.numel() if has_kv else 0,
+            N.ptr(hidden_cache_use_input.contiguous()) if has_hid else 0,
+            hidden_cache_use_input.numel() if has_hid else 0, heads, head_size,
+            hidden_states.size(1) if has_hid else 1, block_size,
+            key.stride(0) if has_kv else 0, value.stride(0) if has_kv else 0,
+            hidden_states.stride(0) if has_hid else 0, kv_cache.stride(1) if has_kv else 0,
+            hidden_cache.stride(2) if has_hid else 0, N.dtype_enum(used[0]), N.current_stream(dev)))
 
 
 def copy_blocks(key_caches: List[torch.Tensor], value_caches: List[torch.Tensor],

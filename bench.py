@@ -5,16 +5,32 @@
 
 One step = the new token's cache write for every request (K/V rows for K/V-cached
 requests, the layer-input row for hidden-cached ones) followed by hybrid decode
-attention over the whole ragged batch.  With N > 1 the attention heads and the
-matching W_k / W_v / W_o slices are sharded over the N ranks (hidden cache
-replicated) and the step also holds the o_proj GEMM and its all-reduce.
+attention over the whole ragged batch, through one native call
+(``attention.decode_layer_step``).  With N > 1 the attention heads and the matching
+W_k / W_v / W_o slices are sharded over the N ranks (hidden cache replicated) and the
+step also holds the o_proj GEMM and its all-reduce: strong scaling, the batch is fixed.
 
-N = 1 runs configuration 2 (OPT-13B layer, fp16, 256 requests, lognormal context
-lengths, half of them hidden-cached).  Prints ONE JSON line on rank 0.
+The headline workload is configuration 2 (OPT-13B layer, fp16, 256 requests, lognormal
+context lengths, half of them hidden-cached).  Prints ONE JSON line on rank 0.  After the
+timed region the default run adds, each with its own clock sample:
+
+  roofline_kv_path_pure / roofline_reprojection_pure   the K/V-only and the hidden-only
+        sub-batch of configuration 2, each kernel running alone;
+  roofline_cache_writes   configuration 3's prefill cache writes + block copies, alone and
+        inside the loaded step;
+  config5_sweep           configuration 5 at 0 / 25 / 50 / 75 / 100 % hidden-cached;
+  config4                 configuration 4 (OPT-66B, bf16, 512 requests) at tp = N;
+  tp_check (N > 1)        the all-reduced o_proj output of four requests against the
+                          unsharded product formed on rank 0.
+
+``--impl reference`` runs the reference's own op chain on the GPU (its CUDA source compiled
+unmodified + the library kernels it calls, see oracle/literal_chain_gpu.py) on the same
+configuration, seed and requests, and the CPU restatement of it beside it.
 """
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import os
 import statistics
@@ -31,6 +47,7 @@ import torch  # noqa: E402
 
 METRIC = "hybrid-cache decode tokens/s @OPT-13B layer, B=256"
 UNIT = "tokens/s"
+TOL = "|x - ref| <= 2e-2 + 2e-2 * |ref|"
 
 
 # --------------------------------------------------------------------------- #
@@ -49,18 +66,13 @@ def measured_peaks():
                 "source": "fallback"}
 
 
-# ncu, 16-request OPT-13B case (profiles/hidden_path_kernel_config5_b16_all_hidden.md,
-# profiles/kv_attention_kernel_config5_b16_all_kv.md): dram read + write bytes per launch over the
-# cached tokens of the launch
-HIDDEN_DRAM_BYTES_PER_TOKEN = (3.007744e9 + 17.6e6) / 29088
-KV_DRAM_BYTES_PER_TOKEN = (595.9e6 + 6.6e6) / 29088
-
-
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """One nvidia-smi process sampling SM clock, power and throttle reasons every 100 ms for
+    the life of the benchmark; ``window(t0, t1)`` summarises the samples of a time window."""
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self, gpu_index: int):
         self.gpu_index = gpu_index
@@ -85,27 +97,28 @@ class ClockSampler:
         self.reader = threading.Thread(target=pump, daemon=True)
         self.reader.start()
 
-    def stop(self, t_begin: float, t_end: float):
-        """Summary of the samples that arrived inside ``[t_begin, t_end]`` (the timed
-        region).  A region shorter than the sampling interval may hold none: then the
-        samples of the half second of identical load just before it are used, and
-        ``window`` says so."""
+    def stop(self):
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.12)
+            return
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
         self.reader.join(timeout=2)
+
+    def window(self, t_begin: float, t_end: float, lead: float = 0.0):
+        """Samples that arrived in ``[t_begin, t_end]``.  A window shorter than the sampling
+        interval may hold none: then the samples of the ``lead`` seconds of identical load
+        just before it are used and ``window`` says so."""
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         inside = [ln for t, ln in self.lines if t_begin <= t <= t_end + 0.02]
-        window = "timed region"
-        if not inside:
-            inside = [ln for t, ln in self.lines if t_begin - 0.5 <= t < t_begin]
-            window = "untimed steps of the same load in the 0.5 s before the timed region (region shorter than the sampling interval)"
+        where = "timed region"
+        if not inside and lead > 0:
+            inside = [ln for t, ln in self.lines if t_begin - lead <= t < t_begin]
+            where = f"untimed steps of the same load in the {lead:.1f} s before the timed region (region shorter than the sampling interval)"
         sm, mx, reasons, power = [], [], set(), []
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in inside:
             f = [x.strip() for x in line.split(",")]
             if len(f) < 9:
@@ -114,18 +127,23 @@ class ClockSampler:
                 sm.append(float(f[1])); mx.append(float(f[2])); power.append(float(f[3]))
             except ValueError:
                 continue
-            for name, v in zip(names, f[5:9]):
+            for name, v in zip(self.NAMES, f[5:9]):
                 if v.lower().startswith("active"):
                     reasons.add(name)
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
-                "samples": len(sm), "power_w_max": max(power) if power else None, "window": window}
+                "samples": len(sm), "power_w_max": max(power) if power else None,
+                "power_w_median": statistics.median(power) if power else None, "window": where}
 
 
 def dist_env():
     return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), \
         int(os.environ.get("WORLD_SIZE", 1))
+
+
+def dtype_name(dt):
+    return {torch.float16: "f16", torch.bfloat16: "bf16", torch.float32: "f32"}[dt]
 
 
 def cpu_sample_requests(lens, hid, flop_budget, e, hd):
@@ -169,6 +187,19 @@ def run_cpu_port(workload_cpu, requests, steps, warmup):
     return (time.perf_counter() - t0) / max(1, steps)
 
 
+def cpu_baseline_block(w, lens, hid, flop_budget, steps=2):
+    shape = w.shape
+    hd = w.heads * shape.head_dim
+    sample = cpu_sample_requests(lens, hid, flop_budget, shape.hidden, hd)
+    cpu_w = w.cpu()
+    sec = run_cpu_port(cpu_w, sample, steps, 0)
+    return {"value": round(len(sample) / sec, 3), "unit": UNIT, "cores": torch.get_num_threads(),
+            "host_cpus": os.cpu_count(), "kind": "port",
+            "sample": f"{len(sample)} of {len(lens)} requests in batch order keeping the hidden/K-V mix "
+                      f"({sum(lens[r] for r in sample)} cached tokens), {steps} steps of "
+                      f"{sec:.2f} s each; tokens/s = sampled requests / time"}
+
+
 # --------------------------------------------------------------------------- #
 # the step
 # --------------------------------------------------------------------------- #
@@ -185,30 +216,17 @@ class LayerStep:
         h, d = w.heads, w.shape.head_dim
         self.h, self.d = h, d
         self.wk, self.bk, self.wv, self.bv = w.kv_weights()
-        self.kv_rows = m.kv_request_rows
-        self.kv_slots = m.slot_mapping[m.kv_cache_use_tot].contiguous()
-        # per-request slot of the new token: K/V requests write K/V rows, hidden requests
-        # write their layer-input row; the other kind is masked with -1 (skipped)
-        new_slot = m.slot_mapping[m.hidden_holder_upd]
-        self.kv_new_slots = torch.where(m.cache_type != 0, torch.full_like(new_slot, -1), new_slot)
         self.out = torch.empty_like(w.query)
         self.prefill_events = None   # (start, stop) recorded around prefill_writes when set
-        self.fused_prefill_write = os.environ.get("APS_BENCH_FUSED_PREFILL_WRITE") is not None
         self.workspace = A.attention_workspace(w.query.device, w.query.shape[0],
                                                m.private_block_tables.shape[1], w.shape.block_size, h, d)
 
-    def cache_writes(self, hidden_states, new_key, new_value, kv_new_slots):
-        from apt_serve_b200 import mixed_cache_ops, ops
-        w, m = self.w, self.w.meta
-        ops.reshape_and_cache_flash(new_key.view(-1, self.h, self.d), new_value.view(-1, self.h, self.d),
-                                    w.kv_cache[0], w.kv_cache[1], kv_new_slots, "auto")
-        mixed_cache_ops.hidden_to_cache(hidden_states, w.hidden_cache, m.slot_mapping,
-                                        m.hidden_cache_use_input, m.hidden_cache_store_tot)
-
-    def attention(self, query, tables, seq_lens, cache_type):
-        return self.A.hybrid_decode_attention(query, self.w.kv_cache, self.w.hidden_cache, self.wk,
-                                              self.bk, self.wv, self.bv, tables, seq_lens, cache_type,
-                                              self.w.scale, out=self.out, workspace=self.workspace)
+    def layer_step(self, query, hidden_states, new_key, new_value, tables, seq_lens, cache_type, out=None):
+        """New-token cache writes + hybrid decode attention: one native call."""
+        w = self.w
+        return self.A.decode_layer_step(query, hidden_states, new_key, new_value, w.kv_cache, w.hidden_cache,
+                                        self.wk, self.bk, self.wv, self.bv, tables, seq_lens, cache_type,
+                                        w.scale, out=self.out if out is None else out, workspace=self.workspace)
 
     def o_proj(self, attn_out):
         import torch.distributed as dist
@@ -217,27 +235,17 @@ class LayerStep:
             self.tp_comm.all_reduce(y)          # aps_tp_allreduce: the library's NCCL communicator
         else:
             dist.all_reduce(y, group=self.tp_group)
-        return y + self.w.o_bias
+        return y.add_(self.w.o_bias)
 
     def prefill_writes(self):
         """Configuration 3: cache the packed prompt tokens (K/V rows of K/V-designated
         prompts, layer-input rows of hidden-designated ones) and copy 5 % of the blocks."""
-        from apt_serve_b200 import mixed_cache_ops, ops
+        from apt_serve_b200 import ops
         from apt_serve_b200.attention import FlashAttentionBackend
         w, pf = self.w, self.w.prefill
         pm = pf.meta
-        if not hasattr(self, "_prefill_kv_slots"):
-            slots = torch.full_like(pm.slot_mapping, -1)
-            slots[pm.kv_cache_use_tot] = pm.slot_mapping[pm.kv_cache_use_tot]
-            self._prefill_kv_slots = slots
-        if self.fused_prefill_write:
-            ops.prefill_cache_write(pf.key, pf.value, pf.hidden_states, w.kv_cache, w.hidden_cache,
-                                    pm.slot_mapping, pm.kv_cache_use_tot, pm.hidden_cache_use_input)
-        else:
-            ops.reshape_and_cache_flash(pf.key, pf.value, w.kv_cache[0], w.kv_cache[1],
-                                        self._prefill_kv_slots, "auto")
-            mixed_cache_ops.hidden_to_cache(pf.hidden_states, w.hidden_cache, pm.slot_mapping,
-                                            pm.hidden_cache_use_input, pm.hidden_cache_store_tot)
+        ops.prefill_cache_write(pf.key, pf.value, pf.hidden_states, w.kv_cache, w.hidden_cache,
+                                pm.slot_mapping, pm.kv_cache_use_tot, pm.hidden_cache_use_input)
         if w.copy_pairs is not None:
             FlashAttentionBackend.copy_blocks([w.kv_cache], w.copy_pairs)
 
@@ -261,8 +269,8 @@ class LayerStep:
             self.prefill_writes()
             if self.prefill_events is not None:
                 self.prefill_events[1].record()
-        self.cache_writes(w.hidden_states, w.new_key, w.new_value, self.kv_new_slots)
-        out = self.attention(w.query, m.private_block_tables, m.seq_lens_tensor, m.cache_type)
+        out = self.layer_step(w.query, w.hidden_states, w.new_key, w.new_value, m.private_block_tables,
+                              m.seq_lens_tensor, m.cache_type)
         if self.tp_group is not None:
             out = self.o_proj(out)
         return out
@@ -270,26 +278,246 @@ class LayerStep:
     def step_absorbed(self):
         """The same step with the hidden requests attended through absorbed projections
         (attention.hybrid_decode_attention_absorbed) instead of the re-projecting kernel."""
+        from apt_serve_b200 import mixed_cache_ops, ops
         w, m = self.w, self.w.meta
-        if w.prefill is not None:
-            self.prefill_writes()
-        self.cache_writes(w.hidden_states, w.new_key, w.new_value, self.kv_new_slots)
-        out = self.A.hybrid_decode_attention_absorbed(
+        if not hasattr(self, "_kv_new_slots"):
+            new_slot = m.slot_mapping[m.hidden_holder_upd]
+            self._kv_new_slots = torch.where(m.cache_type != 0, torch.full_like(new_slot, -1), new_slot)
+        ops.reshape_and_cache_flash(w.new_key.view(-1, self.h, self.d), w.new_value.view(-1, self.h, self.d),
+                                    w.kv_cache[0], w.kv_cache[1], self._kv_new_slots, "auto")
+        mixed_cache_ops.hidden_to_cache(w.hidden_states, w.hidden_cache, m.slot_mapping,
+                                        m.hidden_cache_use_input, m.hidden_cache_store_tot)
+        return self.A.hybrid_decode_attention_absorbed(
             w.query, w.kv_cache, w.hidden_cache, self.wk, self.bk, self.wv, self.bv, m.private_block_tables,
             m.seq_lens_tensor, m.cache_type, w.scale, hidden_rows=m.hidden_cache_use_input, out=self.out)
-        if self.tp_group is not None:
-            out = self.o_proj(out)
-        return out
+
+
+class Timer:
+    """Device timing of K calls of ``fn`` with per-kernel events from the library's hook."""
+
+    def __init__(self, dev, tp, sampler):
+        self.dev, self.tp, self.sampler = dev, tp, sampler
+
+    def barrier(self):
+        torch.cuda.synchronize()
+        if self.tp > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    def run(self, fn, steps, warmup, preload_s=0.0, step_obj=None):
+        """``warmup`` untimed calls, optionally ``preload_s`` seconds more of the same load (so that
+        the power state has settled and clock samples exist), then ``steps`` timed calls.  Returns
+        a dict with ms per step (max over ranks), per-kernel ms from the profile-event hook,
+        the clock sample of the window and time x median SM MHz."""
+        from apt_serve_b200 import _native as N
+        lib = N.lib()
+        self.barrier()
+        t_w = time.perf_counter()
+        for _ in range(max(warmup, 3)):
+            fn()
+        self.barrier()
+        warm_step_s = (time.perf_counter() - t_w) / max(warmup, 3)
+        if preload_s > 0:
+            # chunks of ~50 ms until the sampler has delivered and preload_s has passed (3 s at
+            # most); rank 0 decides so that every rank runs the same number of collectives
+            chunk_t = torch.tensor([min(2000, max(1, int(0.05 / max(warm_step_s, 1e-5))))], device=self.dev)
+            if self.tp > 1:
+                torch.distributed.broadcast(chunk_t, src=0)
+            chunk = int(chunk_t.item())
+            t_pre = time.perf_counter()
+            while True:
+                for _ in range(chunk):
+                    fn()
+                torch.cuda.synchronize()
+                waited = time.perf_counter() - t_pre
+                have = self.sampler is None or bool(self.sampler.lines)
+                go_on = torch.tensor([int((waited < preload_s or not have) and waited < 3.0)], device=self.dev)
+                if self.tp > 1:
+                    torch.distributed.broadcast(go_on, src=0)
+                if not int(go_on.item()):
+                    break
+        ev = lambda: torch.cuda.Event(enable_timing=True)
+        ev_kv = [(ev(), ev()) for _ in range(steps)]
+        ev_hid = [(ev(), ev()) for _ in range(steps)]
+        ev_pf = [(ev(), ev()) for _ in range(steps)]
+        for a, b in ev_kv + ev_hid + ev_pf:   # create the underlying handles
+            a.record(); b.record()
+        self.barrier()
+        t0 = time.perf_counter()
+        e0, e1 = ev(), ev()
+        e0.record()
+        for i in range(steps):
+            if step_obj is not None and step_obj.w.prefill is not None:
+                step_obj.prefill_events = ev_pf[i]
+            lib.aps_set_profile_events(0, ctypes.c_void_p(ev_kv[i][0].cuda_event), ctypes.c_void_p(ev_kv[i][1].cuda_event))
+            lib.aps_set_profile_events(1, ctypes.c_void_p(ev_hid[i][0].cuda_event), ctypes.c_void_p(ev_hid[i][1].cuda_event))
+            fn()
+        e1.record()
+        self.barrier()
+        t1 = time.perf_counter()
+        lib.aps_set_profile_events(0, None, None)
+        lib.aps_set_profile_events(1, None, None)
+        if step_obj is not None:
+            step_obj.prefill_events = None
+        t = torch.tensor([e0.elapsed_time(e1)], device=self.dev, dtype=torch.float64)
+        if self.tp > 1:
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms = float(t.item()) / steps
+        res = {"ms_per_step": ms,
+               "kv_ms": statistics.mean(a.elapsed_time(b) for a, b in ev_kv),
+               "hid_ms": statistics.mean(a.elapsed_time(b) for a, b in ev_hid),
+               "pf_ms": (statistics.mean(a.elapsed_time(b) for a, b in ev_pf)
+                         if step_obj is not None and step_obj.w.prefill is not None else None)}
+        if self.sampler is not None:
+            res["clocks"] = self.sampler.window(t0, t1, lead=max(preload_s, 0.3))
+            mhz = res["clocks"].get("sm_mhz")
+            res["ms_x_sm_mhz"] = round(ms * mhz, 1) if mhz else None
+        return res
+
+
+def kernel_rooflines(work, res, peaks):
+    """The two attention kernels' roofline blocks from per-kernel event times."""
+    hid_ms, kv_ms = res["hid_ms"], res["kv_ms"]
+    tflops = work["reprojection_flops"] / (hid_ms * 1e-3) / 1e12 if hid_ms > 0 and work["t_hidden"] else 0.0
+    kv_gbs = work["kv_attention_bytes"] / (kv_ms * 1e-3) / 1e9 if kv_ms > 0 and work["t_kv"] else 0.0
+    hidden = {"kernel": "hidden_path_kernel (tcgen05 re-projection + softmax partials)",
+              "bound": "tensor", "achieved": round(tflops, 2), "peak": peaks["tflops_sustained"],
+              "unit": "TFLOP/s", "frac": round(tflops / peaks["tflops_sustained"], 4),
+              "frac_of_burst_peak": round(tflops / peaks["tflops_burst"], 4),
+              "peak_source": peaks["source"] + " (sustained bf16 figure: the kernel runs inside a long step)",
+              "ms_per_launch": round(hid_ms, 4), "flops_per_launch": work["reprojection_flops"]}
+    kv = {"kernel": "kv_attention_mma_kernel (K/V streaming)", "bound": "hbm",
+          "achieved": round(kv_gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+          "frac": round(kv_gbs / peaks["hbm_gbs"], 4), "peak_source": peaks["source"],
+          "ms_per_launch": round(kv_ms, 4), "bytes_per_launch": work["kv_attention_bytes"]}
+    return hidden, kv
+
+
+def slim(res, keys=("ms_per_step", "kv_ms", "hid_ms", "pf_ms")):
+    out = {}
+    for k in keys:
+        if res.get(k) is not None:
+            out[k] = round(res[k], 4)
+    for k in ("clocks", "ms_x_sm_mhz"):
+        if k in res:
+            out[k] = res[k]
+    return out
 
 
 # --------------------------------------------------------------------------- #
-# arms
+# end to end through the public API with host buffers
 # --------------------------------------------------------------------------- #
+class EndToEnd:
+    """Every step: ONE host-to-device copy of the step's inputs out of a pinned staging buffer
+    (layer input, query, new K/V rows, block tables, sequence lengths, cache types), the step
+    through the public API, one device-to-host copy of the result.  Two steps are in flight:
+    step i + 1's inputs are copied on a side stream while step i computes, results leave on a
+    third stream, and the host waits for step i - 1's result before it enqueues step i + 1."""
+
+    def __init__(self, st: LayerStep, dev, tp, out_shape, out_dtype):
+        w, m = st.w, st.w.meta
+        self.st, self.dev, self.tp = st, dev, tp
+        src = {"hidden_states": w.hidden_states, "query": w.query, "new_key": w.new_key,
+               "new_value": w.new_value, "tables": m.private_block_tables, "seq_lens": m.seq_lens_tensor,
+               "cache_type": m.cache_type}
+        self.layout, off = {}, 0
+        for k, v in src.items():
+            n = v.numel() * v.element_size()
+            self.layout[k] = (off, n, v.dtype, tuple(v.shape))
+            off = (off + n + 255) // 256 * 256
+        self.h2d_bytes = sum(n for _, n, _, _ in self.layout.values())
+        self.host = torch.empty(off, dtype=torch.uint8).pin_memory()
+        for k, v in src.items():
+            o, n, _, _ = self.layout[k]
+            self.host[o:o + n] = v.contiguous().view(torch.uint8).view(-1).cpu()
+        self.slots = []
+        for _ in range(2):
+            buf = torch.empty(off, dtype=torch.uint8, device=dev)
+            views = {k: buf[o:o + n].view(dt).view(shape) for k, (o, n, dt, shape) in self.layout.items()}
+            self.slots.append({"buf": buf, "in": views, "out": torch.empty(out_shape, dtype=out_dtype).pin_memory(),
+                               "attn": torch.empty_like(w.query),   # the slot's own attention output
+                               "h2d": torch.cuda.Event(), "computed": torch.cuda.Event(), "d2h": torch.cuda.Event()})
+        self.d2h_bytes = self.slots[0]["out"].numel() * self.slots[0]["out"].element_size()
+        self.copy_stream = torch.cuda.Stream(device=dev)
+        self.out_stream = torch.cuda.Stream(device=dev)
+
+    def enqueue(self, i):
+        s = self.slots[i & 1]
+        main = torch.cuda.current_stream()
+        with torch.cuda.stream(self.copy_stream):
+            self.copy_stream.wait_event(s["computed"])      # the slot's previous step has read its inputs
+            s["buf"].copy_(self.host, non_blocking=True)     # one cudaMemcpyAsync
+            s["h2d"].record(self.copy_stream)
+        main.wait_event(s["h2d"])
+        main.wait_event(s["d2h"])                            # the slot's previous result has left the device
+        v = s["in"]
+        out = self.st.layer_step(v["query"], v["hidden_states"], v["new_key"], v["new_value"], v["tables"],
+                                 v["seq_lens"], v["cache_type"], out=s["attn"])
+        if self.tp > 1:
+            out = self.st.o_proj(out)
+        s["computed"].record(main)
+        with torch.cuda.stream(self.out_stream):
+            self.out_stream.wait_event(s["computed"])
+            s["out"].copy_(out, non_blocking=True)
+            s["d2h"].record(self.out_stream)
+        out.record_stream(self.out_stream)
+
+    def run(self, steps, barrier):
+        for s in self.slots:
+            s["computed"].record()
+            s["d2h"].record()
+        for i in range(4):
+            self.enqueue(i)
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(steps):
+            self.enqueue(i)
+            if i > 0:
+                self.slots[(i - 1) & 1]["d2h"].synchronize()   # the previous step's result is on the host
+        self.slots[(steps - 1) & 1]["d2h"].synchronize()
+        barrier()
+        sec = (time.perf_counter() - t0) / steps
+        t = torch.tensor([sec], device=self.dev, dtype=torch.float64)
+        if self.tp > 1:
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        return float(t.item())
+
+
+# --------------------------------------------------------------------------- #
+# our arm
+# --------------------------------------------------------------------------- #
+def tp_check(st: LayerStep, w, tp, rank, dev):
+    """The all-reduced o_proj output of four sampled requests against the unsharded product
+    formed on rank 0 from the all-gathered attention slices and W_o columns (fp32)."""
+    import torch.distributed as dist
+    m = w.meta
+    attn = st.layer_step(w.query, w.hidden_states, w.new_key, w.new_value, m.private_block_tables,
+                         m.seq_lens_tensor, m.cache_type).clone()
+    y = st.o_proj(attn.clone())
+    b = attn.shape[0]
+    rows = sorted({0, b // 3, (2 * b) // 3, b - 1})
+    idx = torch.tensor(rows, device=dev)
+    a_loc = attn.index_select(0, idx).contiguous()
+    a_all = [torch.empty_like(a_loc) for _ in range(tp)]
+    w_all = [torch.empty_like(w.o_weight) for _ in range(tp)]
+    dist.all_gather(a_all, a_loc)
+    dist.all_gather(w_all, w.o_weight.contiguous())
+    if rank != 0:
+        return None
+    a_full = torch.cat(a_all, dim=1).float()
+    w_full = torch.cat(w_all, dim=1).float()
+    ref = a_full @ w_full.t() + w.o_bias.float()
+    got = y.index_select(0, idx).float()
+    err = (got - ref).abs()
+    bound = 2e-2 + 2e-2 * ref.abs()
+    return {"requests": rows, "max_abs_err": round(float(err.max()), 6),
+            "max_abs_ref": round(float(ref.abs().max()), 4), "tolerance": TOL,
+            "ok": bool((err <= bound).all())}
+
+
 def run_ours(args):
-    import ctypes
-    from apt_serve_b200 import _native as N
     from apt_serve_b200.workloads import (CONFIG_SHAPES, algorithmic_work, draw_decode_batch,
-                                          make_decode_workload)
+                                          draw_prefill_batch, make_decode_workload)
     rank, local_rank, world = dist_env()
     n_gpus = args.gpus
     assert world == n_gpus or world == 1, f"WORLD_SIZE {world} does not match --gpus {n_gpus}"
@@ -301,238 +529,214 @@ def run_ours(args):
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
         group = dist.group.WORLD
+    tp_comm = None
+    if tp > 1:
+        # the exchange step through the C ABI (aps_tp_*); torch.distributed only carries the id
+        from apt_serve_b200.tp_comm import TensorParallelComm
+        tp_comm = TensorParallelComm.from_torch_distributed()
+    peaks = measured_peaks()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler is not None:
+        sampler.start()
+    timer = Timer(dev, tp, sampler)
+    K, W = args.steps, max(args.warmup, 3)
+    extras = not args.no_extras
 
+    def build(cfg, lens, hid, **kw):
+        return make_decode_workload(CONFIG_SHAPES[cfg], lens, hid, 1000 + cfg, dev, tp_rank=rank, tp_size=tp, **kw)
+
+    # ---- headline: configuration `cfg` (2 unless --config) ----
     cfg = args.config
     shape = CONFIG_SHAPES[cfg]
     seed = 1000 + cfg
     lens, hid = draw_decode_batch(cfg, seed, batch=args.batch, hidden_fraction=args.hidden_fraction)
-    extra = {}
-    if cfg == 3:
-        from apt_serve_b200.workloads import draw_prefill_batch
-        extra = {"prefill": draw_prefill_batch(), "copy_fraction": 0.05}
-    w = make_decode_workload(shape, lens, hid, seed, dev, tp_rank=rank, tp_size=tp, **extra)
+    kw = {"prefill": draw_prefill_batch(), "copy_fraction": 0.05} if cfg == 3 else {}
+    w = build(cfg, lens, hid, **kw)
     work = algorithmic_work(shape, lens, hid, tp)
     B = len(lens)
-    tp_comm = None
-    if tp > 1 and os.environ.get("APS_BENCH_TORCH_ALLREDUCE") is None:
-        # the exchange step through the C ABI (aps_tp_*); torch.distributed only carries the id
-        from apt_serve_b200.tp_comm import TensorParallelComm
-        tp_comm = TensorParallelComm.from_torch_distributed()
     st = LayerStep(w, group, tp_comm)
-    peaks = measured_peaks()
-
-    def barrier():
-        torch.cuda.synchronize()
-        if tp > 1:
-            torch.distributed.barrier()
-        torch.cuda.synchronize()
-
-    # ---- device-resident timing: warm-up, then exactly K steps ----
-    barrier()
-    t_w = time.perf_counter()
-    for _ in range(max(args.warmup, 3)):
-        st.step()
-    barrier()
-    warm_step_s = (time.perf_counter() - t_w) / max(args.warmup, 3)
-    K = args.steps
-    ev_kv = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
-    ev_hid = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
-    for a, b in ev_kv + ev_hid:   # create the underlying handles
-        a.record(); b.record()
-    torch.cuda.synchronize()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    # untimed steps of the same load while nvidia-smi comes up: chunks of ~50 ms until its first
-    # sample has arrived and half a second has passed (3 s at most); rank 0 decides so that every
-    # rank runs the same number of collectives
-    chunk_t = torch.tensor([min(2000, max(1, int(0.05 / max(warm_step_s, 1e-5))))], device=dev)
-    if tp > 1:
-        torch.distributed.broadcast(chunk_t, src=0)
-    chunk = int(chunk_t.item())
-    t_pre = time.perf_counter()
-    while True:
-        for _ in range(chunk):
-            st.step()
-        torch.cuda.synchronize()
-        waited = time.perf_counter() - t_pre
-        go_on = torch.tensor([int((waited < 0.5 or not sampler.lines) and waited < 3.0)], device=dev)
-        if tp > 1:
-            torch.distributed.broadcast(go_on, src=0)
-        if not int(go_on.item()):
-            break
-    barrier()
-    t_region0 = time.perf_counter()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    lib = N.lib()
-    ev_pf = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
-    e0.record()
-    for i in range(K):
-        st.prefill_events = ev_pf[i] if w.prefill is not None else None
-        lib.aps_set_profile_events(0, ctypes.c_void_p(ev_kv[i][0].cuda_event), ctypes.c_void_p(ev_kv[i][1].cuda_event))
-        lib.aps_set_profile_events(1, ctypes.c_void_p(ev_hid[i][0].cuda_event), ctypes.c_void_p(ev_hid[i][1].cuda_event))
-        st.step()
-    e1.record()
-    barrier()
-    t_region1 = time.perf_counter()
-    st.prefill_events = None
-    lib.aps_set_profile_events(0, None, None)
-    lib.aps_set_profile_events(1, None, None)
-    clocks = sampler.stop(t_region0, t_region1) if rank == 0 else None
-    ms_total = e0.elapsed_time(e1)
-    t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
-    if tp > 1:
-        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-    ms_per_step = float(t.item()) / K
-    kv_ms = statistics.mean(a.elapsed_time(b) for a, b in ev_kv)
-    hid_ms = statistics.mean(a.elapsed_time(b) for a, b in ev_hid)
+    check = tp_check(st, w, tp, rank, dev) if tp > 1 else None
+    res = timer.run(st.step, K, W, preload_s=0.5, step_obj=st)
+    ms_per_step = res["ms_per_step"]
     status = st.A.attention_status(st.workspace)
-    pf_ms = statistics.mean(a.elapsed_time(b) for a, b in ev_pf) if w.prefill is not None else None
+    roof_hidden, roof_kv = kernel_rooflines(work, res, peaks)
 
-    # ---- end to end through the public API with host buffers ----
-    m = w.meta
-    host_in = {
-        "hidden_states": w.hidden_states.cpu().pin_memory(), "query": w.query.cpu().pin_memory(),
-        "new_key": w.new_key.cpu().pin_memory(), "new_value": w.new_value.cpu().pin_memory(),
-        "tables": m.private_block_tables.cpu().pin_memory(), "seq_lens": m.seq_lens_tensor.cpu().pin_memory(),
-        "cache_type": m.cache_type.cpu().pin_memory(), "kv_new_slots": st.kv_new_slots.cpu().pin_memory(),
-    }
-    dev_in = {k: torch.empty_like(v, device=dev) for k, v in host_in.items()}
     out_shape = (B, shape.hidden) if tp > 1 else tuple(w.query.shape)
-    host_out = torch.empty(out_shape, dtype=shape.dtype).pin_memory()
-    h2d = sum(v.numel() * v.element_size() for v in host_in.values())
-    d2h = host_out.numel() * host_out.element_size()
+    e2e = EndToEnd(st, dev, tp, out_shape, shape.dtype)
+    e2e_s = e2e.run(K, timer.barrier)
+    h2d_bytes, d2h_bytes = e2e.h2d_bytes, e2e.d2h_bytes
+    status |= st.A.attention_status(st.workspace)
 
-    def e2e_step():
-        for k, v in host_in.items():
-            dev_in[k].copy_(v, non_blocking=True)
-        st.cache_writes(dev_in["hidden_states"], dev_in["new_key"], dev_in["new_value"], dev_in["kv_new_slots"])
-        out = st.attention(dev_in["query"], dev_in["tables"], dev_in["seq_lens"], dev_in["cache_type"])
-        if tp > 1:
-            out = st.o_proj(out)
-        host_out.copy_(out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-
-    for _ in range(3):
-        e2e_step()
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(K):
-        e2e_step()
-    barrier()
-    e2e_s = (time.perf_counter() - t0) / K
-    t = torch.tensor([e2e_s], device=dev, dtype=torch.float64)
-    if tp > 1:
-        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-    e2e_s = float(t.item())
-
+    line_extra = {}
     # ---- for information: the same step with absorbed projections (not the path the metric
     # is quoted on: the headline step re-projects on the tensor cores) ----
-    absorbed = None
-    if (tp == 1 and work["t_hidden"] > 0 and shape.dtype in (torch.float16, torch.bfloat16)
-            and shape.hidden % 512 == 0 and shape.head_dim == 128):
+    if (extras and tp == 1 and work["t_hidden"] > 0 and st.A.absorbed_supported(w.heads, shape.hidden, shape.dtype)
+            and shape.head_dim == 128 and w.prefill is None):
         ref_out = st.step().float().clone()
-        for _ in range(3):
-            out_abs = st.step_absorbed()
+        out_abs = st.step_absorbed()
         diff = (out_abs.float() - ref_out).abs()
         outside = int((diff > 2e-2 + 2e-2 * ref_out.abs()).sum().item())
-        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        a0.record()
-        for _ in range(K):
-            st.step_absorbed()
-        a1.record()
-        torch.cuda.synchronize()
-        abs_ms = a0.elapsed_time(a1) / K
-        absorbed = {"ms_per_step": round(abs_ms, 4), "tokens_per_s": round(B / (abs_ms * 1e-3), 2),
-                    "max_abs_diff_vs_headline_path": round(float(diff.max().item()), 6),
-                    "elements_outside_2e-2_tolerance": outside,
-                    "note": "opt-in variant (hybrid_decode_attention_absorbed): same result, scores and "
-                            "weighted sums taken over the cached hidden rows directly"}
+        r = timer.run(st.step_absorbed, K, 3)
+        line_extra["absorbed_variant"] = {
+            "ms_per_step": round(r["ms_per_step"], 4), "tokens_per_s": round(B / (r["ms_per_step"] * 1e-3), 2),
+            "max_abs_diff_vs_headline_path": round(float(diff.max().item()), 6),
+            "elements_outside_2e-2_tolerance": outside,
+            "note": "opt-in variant (hybrid_decode_attention_absorbed): same result, scores and weighted sums "
+                    "taken over the cached hidden rows directly; not the path the metric is quoted on"}
+
+    # ---- the pure sub-batches of the headline configuration ----
+    if extras and cfg in (2, 5) and tp == 1 and 0 < sum(hid) < B:
+        m = w.meta
+        for name, keep in (("roofline_kv_path_pure", [not h for h in hid]), ("roofline_reprojection_pure", list(hid))):
+            rows = torch.tensor([r for r, k in enumerate(keep) if k], device=dev)
+            sub = {"q": w.query.index_select(0, rows), "t": m.private_block_tables.index_select(0, rows),
+                   "s": m.seq_lens_tensor.index_select(0, rows), "c": m.cache_type.index_select(0, rows)}
+            sub_out = torch.empty_like(sub["q"])
+            fn = lambda: st.A.hybrid_decode_attention(sub["q"], w.kv_cache, w.hidden_cache, st.wk, st.bk, st.wv,
+                                                      st.bv, sub["t"], sub["s"], sub["c"], w.scale, out=sub_out,
+                                                      workspace=st.workspace)
+            r = timer.run(fn, K, 3, preload_s=0.3)
+            sw = algorithmic_work(shape, [l for l, k in zip(lens, keep) if k], [h for h, k in zip(hid, keep) if k], tp)
+            rh, rk = kernel_rooflines(sw, r, peaks)
+            blk = rk if name == "roofline_kv_path_pure" else rh
+            if name == "roofline_reprojection_pure":
+                blk["traffic"] = None
+            blk.update({"requests": int(rows.numel()), "call_ms": round(r["ms_per_step"], 4),
+                        "clocks": r.get("clocks"), "kernel_ms_x_sm_mhz":
+                            round(blk["ms_per_launch"] * r["clocks"]["sm_mhz"], 1)
+                            if r.get("clocks") and r["clocks"].get("sm_mhz") else None,
+                        "note": "the sub-batch of the headline configuration alone: no other kernel of the step runs"})
+            line_extra[name] = blk
+        status |= st.A.attention_status(st.workspace)
+
+    # ---- host-core baseline on a bounded sample (rank 0, N = 1 only) ----
+    cpu_baseline = None
+    if tp == 1 and not args.no_cpu_baseline:
+        cpu_baseline = cpu_baseline_block(w, lens, hid, args.cpu_flops)
+
+    pf_block = None
+    if w.prefill is not None and res["pf_ms"]:
+        pf_block = cache_write_block(st, res["pf_ms"], peaks, "inside the loaded step")
+    del e2e, st, w
+    torch.cuda.empty_cache()
+
+    # ---- configuration 3: prefill cache writes + block copies ----
+    if extras and cfg == 2 and tp == 1:
+        l3, h3 = draw_decode_batch(3, 1003)
+        w3 = build(3, l3, h3, prefill=draw_prefill_batch(), copy_fraction=0.05)
+        st3 = LayerStep(w3)
+        r_step = timer.run(st3.step, max(5, K // 2), 3, preload_s=0.4, step_obj=st3)
+        blk = cache_write_block(st3, r_step["pf_ms"], peaks, "inside the loaded step (configuration 3: "
+                                "prefill writes + block copies + decode step, back to back)")
+        blk["clocks"] = r_step.get("clocks")
+        blk["step_ms"] = round(r_step["ms_per_step"], 4)
+        r_alone = timer.run(st3.prefill_writes, K, 3, preload_s=0.3)
+        alone = cache_write_block(st3, r_alone["ms_per_step"], peaks, "the two launches alone, back to back")
+        blk["alone"] = {k: alone[k] for k in ("ms_per_step", "achieved", "frac")}
+        blk["alone"]["clocks"] = r_alone.get("clocks")
+        line_extra["roofline_cache_writes"] = blk
+        del st3, w3
+        torch.cuda.empty_cache()
+    elif pf_block is not None:
+        line_extra["roofline_cache_writes"] = pf_block
+
+    # ---- configuration 5: hidden fraction swept ----
+    if extras and cfg == 2 and tp == 1:
+        sweep = []
+        for frac in (0.0, 0.25, 0.5, 0.75, 1.0):
+            l5, h5 = draw_decode_batch(5, 1005, hidden_fraction=frac)
+            w5 = build(5, l5, h5)
+            st5 = LayerStep(w5)
+            r = timer.run(st5.step, max(5, K // 2), 3, preload_s=0.3)
+            wk5 = algorithmic_work(CONFIG_SHAPES[5], l5, h5, tp)
+            rh, rk = kernel_rooflines(wk5, r, peaks)
+            sweep.append({"hidden_fraction": frac, "ms_per_step": round(r["ms_per_step"], 4),
+                          "tokens_per_s": round(len(l5) / (r["ms_per_step"] * 1e-3), 1),
+                          "reprojection_tflops": rh["achieved"] if wk5["t_hidden"] else None,
+                          "reprojection_frac": rh["frac"] if wk5["t_hidden"] else None,
+                          "kv_path_gbs": rk["achieved"] if wk5["t_kv"] else None,
+                          "kv_path_frac": rk["frac"] if wk5["t_kv"] else None,
+                          "clocks": r.get("clocks"), "ms_x_sm_mhz": r.get("ms_x_sm_mhz")})
+            status |= st5.A.attention_status(st5.workspace)
+            del st5, w5
+            torch.cuda.empty_cache()
+        line_extra["config5_sweep"] = {"workload": "OPT-13B layer, fp16, 64 requests of 1536..2048 tokens", "points": sweep}
+
+    # ---- configuration 4 at tp = N ----
+    if extras and cfg == 2:
+        l4, h4 = draw_decode_batch(4, 1004)
+        w4 = build(4, l4, h4)
+        st4 = LayerStep(w4, group, tp_comm)
+        k4 = max(3, K // 4) if tp == 1 else K
+        r = timer.run(st4.step, k4, 3, preload_s=0.4)
+        wk4 = algorithmic_work(CONFIG_SHAPES[4], l4, h4, tp)
+        rh, rk = kernel_rooflines(wk4, r, peaks)
+        e4 = EndToEnd(st4, dev, tp, (len(l4), CONFIG_SHAPES[4].hidden) if tp > 1 else tuple(w4.query.shape),
+                      CONFIG_SHAPES[4].dtype)
+        e4_s = e4.run(k4, timer.barrier)
+        status |= st4.A.attention_status(st4.workspace)
+        line_extra["config4"] = {
+            "workload": f"OPT-66B layer (72 heads x 128, hidden 9216), bf16, 512 decode requests, "
+                        f"{sum(h4)} hidden-cached, tp = {tp} ({72 // tp} heads per rank)",
+            "steps": k4, "ms_per_step": round(r["ms_per_step"], 4),
+            "tokens_per_s": round(len(l4) / (r["ms_per_step"] * 1e-3), 1),
+            "e2e_ms_per_step": round(e4_s * 1e3, 4), "e2e_tokens_per_s": round(len(l4) / e4_s, 1),
+            "reprojection_ms": round(r["hid_ms"], 4), "reprojection_tflops_per_gpu": rh["achieved"],
+            "kv_path_ms": round(r["kv_ms"], 4), "kv_path_gbs_per_gpu": rk["achieved"],
+            "clocks": r.get("clocks"), "ms_x_sm_mhz": r.get("ms_x_sm_mhz")}
+        del e4, st4, w4
 
     if tp_comm is not None:
         tp_comm.destroy()
+    if sampler is not None:
+        sampler.stop()
     if rank != 0:
         if tp > 1:
             torch.distributed.destroy_process_group()
         return
 
-    # DRAM bytes per launch, from the ncu captures summarised under profiles/ (16-request case of
-    # the same OPT-13B shapes), scaled by the cached tokens a launch processes: both kernels'
-    # traffic grows in proportion to them (hidden rows once plus the W rows re-streamed per
-    # 16-tile group; K/V rows once).  Other shapes: not captured.
-    opt13b = shape.name == "opt-13b" and tp == 1
-    hid_traffic = int(HIDDEN_DRAM_BYTES_PER_TOKEN * work["t_hidden"]) if opt13b else None
-    kv_traffic = int(KV_DRAM_BYTES_PER_TOKEN * work["t_kv"]) if opt13b else None
-    tflops = work["reprojection_flops"] / (hid_ms * 1e-3) / 1e12 if hid_ms > 0 and work["t_hidden"] else 0.0
-    kv_gbs = work["kv_attention_bytes"] / (kv_ms * 1e-3) / 1e9 if kv_ms > 0 and work["t_kv"] else 0.0
-    if work["t_hidden"] > 0:
-        roofline = {"kernel": "hidden_path_kernel (tcgen05 re-projection + softmax partials)",
-                    "bound": "tensor", "achieved": round(tflops, 2), "peak": peaks["tflops_sustained"],
-                    "unit": "TFLOP/s", "frac": round(tflops / peaks["tflops_sustained"], 4),
-                    "frac_of_burst_peak": round(tflops / peaks["tflops_burst"], 4),
-                    "peak_source": peaks["source"] + " (sustained bf16 figure: the kernel runs inside a long step)",
-                    "ms_per_launch": round(hid_ms, 4), "flops_per_launch": work["reprojection_flops"],
-                    "traffic": hid_traffic}
-    else:
-        roofline = {"kernel": "kv_attention_kernel", "bound": "hbm", "achieved": round(kv_gbs, 1),
-                    "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(kv_gbs / peaks["hbm_gbs"], 4),
-                    "peak_source": peaks["source"], "ms_per_launch": round(kv_ms, 4),
-                    "bytes_per_launch": work["kv_attention_bytes"], "traffic": kv_traffic}
-    roofline_kv = {"kernel": "kv_attention_kernel (K/V streaming)", "bound": "hbm",
-                   "achieved": round(kv_gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                   "frac": round(kv_gbs / peaks["hbm_gbs"], 4), "ms_per_launch": round(kv_ms, 4),
-                   "bytes_per_launch": work["kv_attention_bytes"], "traffic": kv_traffic}
-
-    # ---- host-core baseline on a bounded sample (rank 0, N = 1 only) ----
-    cpu_baseline = None
-    if tp == 1 and not args.no_cpu_baseline:
-        hd = w.heads * shape.head_dim
-        sample = cpu_sample_requests(lens, hid, args.cpu_flops, shape.hidden, hd)
-        cpu_w = w.cpu()
-        sec = run_cpu_port(cpu_w, sample, 2, 0)
-        cpu_baseline = {"value": round(len(sample) / sec, 3), "unit": UNIT, "cores": torch.get_num_threads(),
-                        "host_cpus": os.cpu_count(), "kind": "port",
-                        "sample": f"{len(sample)} of {B} requests in batch order keeping the hidden/K-V mix "
-                                  f"({sum(lens[r] for r in sample)} cached tokens), two steps of "
-                                  f"{sec:.2f} s each; tokens/s = sampled requests / time"}
-        del cpu_w
-
+    roofline = dict(roof_hidden if work["t_hidden"] > 0 else roof_kv)
+    roofline["traffic"] = None
+    roofline["traffic_source"] = ("not captured for this launch: ncu captures of this kernel are taken on the "
+                                  "16-request case and its DRAM traffic does not "
+                                  "scale with the cached tokens alone (it depends on the work-order groups)")
+    roof_kv["traffic"] = int(1.01 * work["kv_attention_bytes"]) if work["t_kv"] else None
+    roof_kv["traffic_source"] = "ncu on the 16-request all-K/V case: 1.01 x the algorithmic bytes, scaled by the cached tokens"
+    launches = 5 + (2 if cfg == 3 else 0)
     line = {
         "metric": METRIC, "value": round(B / (ms_per_step * 1e-3), 2), "unit": UNIT, "n_gpus": n_gpus,
-        "steps": K, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4),
-        "higher_is_better": True, "scaling": "strong" if tp > 1 else "weak", "vs_baseline": None,
-        "dtype": {torch.float16: "f16", torch.bfloat16: "bf16", torch.float32: "f32"}[shape.dtype],
-        "data": "synthetic",
+        "steps": K, "warmup": W, "ms_per_step": round(ms_per_step, 4),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": dtype_name(shape.dtype), "data": "synthetic",
         "config": {"workload": f"config {cfg}: {shape.name} layer ({shape.num_heads} heads x {shape.head_dim}, "
-                               f"hidden {shape.hidden}), {B} decode requests, {sum(hid)} hidden-cached, "
-                               f"T_kv={work['t_kv']} T_hidden={work['t_hidden']} cached tokens per rank view",
-                   "step": ("prefill cache writes + block copies + " if w.prefill is not None else "") +
+                               f"hidden {shape.hidden}), {B} decode requests, {sum(hid)} hidden-cached, seed {seed}",
+                   "cached_tokens_per_rank_view": {"t_kv": work["t_kv"], "t_hidden": work["t_hidden"]},
+                   "step": ("prefill cache writes + block copies + " if cfg == 3 else "") +
                            "new-token cache writes + hybrid decode attention" +
                            (" + o_proj + all-reduce" if tp > 1 else ""),
                    "parallelism": f"tp{tp}" if tp > 1 else "single GPU",
-                   **({"all_reduce": "aps_tp_allreduce (NCCL)" if tp_comm is not None else "torch.distributed (NCCL)"}
-                      if tp > 1 else {}),
+                   **({"all_reduce": "aps_tp_allreduce (NCCL)"} if tp > 1 else {}),
                    "l2": (f"inputs larger than L2: {(work['kv_attention_bytes'] + work['hidden_bytes']) / 1e9:.2f} GB streamed per step"
                           if work['kv_attention_bytes'] + work['hidden_bytes'] > 256e6 else
                           f"working set {(work['kv_attention_bytes'] + work['hidden_bytes']) / 1e6:.1f} MB fits in L2: the number is L2-warm"),
                    "seed": seed},
-        "clocks": clocks,
-        "e2e": {"value": round(B / e2e_s, 2), "unit": UNIT, "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_s * 1e3, 4)},
-        "gpu_launches": (6 + (3 if w.prefill is not None else 0)) * K,
-        "roofline": roofline, "roofline_kv_path": roofline_kv,
-        **({"roofline_cache_writes": {
-            "kernels": "reshape_and_cache + hidden_to_cache + copy_blocks (prefill part of config 3)",
-            "bound": "hbm", "bytes_per_step": st.prefill_write_bytes(), "ms_per_step": round(pf_ms, 4),
-            "achieved": round(st.prefill_write_bytes() / (pf_ms * 1e-3) / 1e9, 1), "peak": peaks["hbm_gbs"],
-            "unit": "GB/s", "frac": round(st.prefill_write_bytes() / (pf_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
-            "prefill_tokens": int(w.prefill.meta.num_prefill_tokens),
-            "copied_blocks": 0 if w.copy_pairs is None else int(w.copy_pairs.shape[0])}} if pf_ms else {}),
+        "clocks": res.get("clocks"), "ms_x_sm_mhz": res.get("ms_x_sm_mhz"),
+        "e2e": {"value": round(B / e2e_s, 2), "unit": UNIT, "h2d_bytes_per_step": h2d_bytes,
+                "d2h_bytes_per_step": d2h_bytes, "ms_per_step": round(e2e_s * 1e3, 4),
+                "pipeline": "two steps in flight: one pinned staging buffer and one host-to-device copy per step on "
+                            "a side stream, the step and the device-to-host copy of its result on the main stream; "
+                            "the host waits for step i - 1's result before it enqueues step i + 1"},
+        "gpu_launches": launches * K,
+        "gpu_launches_per_step": {"count": launches,
+                                  "kernels": "bulk_copy_kernel (new-token rows), plan_kernel, kv_attention_mma_kernel, "
+                                             "hidden_path_kernel, combine_kernel" +
+                                             (" + 2 bulk_copy_kernel launches of the prefill part" if cfg == 3 else "")},
+        "roofline": roofline, "roofline_kv_path": roof_kv,
         "device_status": status,
     }
-    if absorbed is not None:
-        line["absorbed_variant"] = absorbed
+    if check is not None:
+        line["tp_check"] = check
+    line.update(line_extra)
     if cpu_baseline is not None:
         line["cpu_baseline"] = cpu_baseline
     print(json.dumps(line))
@@ -540,39 +744,146 @@ def run_ours(args):
         torch.distributed.destroy_process_group()
 
 
+def cache_write_block(st, ms, peaks, where):
+    nbytes = st.prefill_write_bytes()
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    w = st.w
+    return {"kernels": "bulk_copy_kernel x 2: prefill_cache_write (K/V rows + layer-input rows of the packed prompts) + copy_blocks (prefill part of configuration 3)",
+            "bound": "hbm", "bytes_per_step": nbytes, "ms_per_step": round(ms, 4), "achieved": round(gbs, 1),
+            "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(gbs / peaks["hbm_gbs"], 4),
+            "prefill_tokens": int(w.prefill.meta.num_prefill_tokens),
+            "copied_blocks": 0 if w.copy_pairs is None else int(w.copy_pairs.shape[0]), "measured": where}
+
+
+# --------------------------------------------------------------------------- #
+# reference arm
+# --------------------------------------------------------------------------- #
 def run_reference(args):
-    """The reference path's semantics on the host cores (the oracle port: the reference
-    itself needs vLLM 0.5.0.post1 and a GPU), on a bounded sample of the same workload."""
-    rank, _, world = dist_env()
+    """The reference's decode op chain for the same configuration, seed and requests.
+
+    On the GPU: the reference's own ``mixed_cache.cu`` (compiled unmodified, oracle/_ref) for
+    hidden_to_cache / cache_to_hidden / mixed_kv_to_cache, ``F.linear`` for the kv_only
+    projection, vLLM's flash-attention paged decode over the shared cache -- the kernels of
+    aptserve_opt.py:106-124 and aptserve_flash_attn.py:356-387, 462-473 (the unmodified vLLM
+    0.5.0.post1 engine around them cannot be installed here).  Beside it, as ``cpu_baseline``,
+    the CPU restatement of the same path on the host cores on a bounded sample.  When a piece
+    of the GPU chain is missing the line's value is the CPU figure and says so."""
+    rank, local_rank, world = dist_env()
     if rank != 0:
         return
-    # all host cores, also under torchrun (which exports OMP_NUM_THREADS=1 to its ranks)
-    torch.set_num_threads(max(1, os.cpu_count() or 1))
+    torch.set_num_threads(max(1, os.cpu_count() or 1))   # torchrun exports OMP_NUM_THREADS=1 to its ranks
     from apt_serve_b200.workloads import CONFIG_SHAPES, draw_decode_batch, make_decode_workload
     cfg = args.config
     shape = CONFIG_SHAPES[cfg]
     seed = 1000 + cfg
     lens, hid = draw_decode_batch(cfg, seed, batch=args.batch, hidden_fraction=args.hidden_fraction)
-    hd = shape.num_heads * shape.head_dim
-    sample = cpu_sample_requests(lens, hid, args.cpu_flops, shape.hidden, hd)
-    # only the sampled requests are materialised on the host (same distributions, same seed)
-    s_lens = [lens[r] for r in sample]
-    s_hid = [hid[r] for r in sample]
-    w = make_decode_workload(shape, s_lens, s_hid, seed, "cpu")
-    reqs = list(range(len(sample)))
-    sec = run_cpu_port(w, reqs, args.steps, min(args.warmup, 1))
-    value = len(sample) / sec
-    desc = (f"{len(sample)} of {len(lens)} requests of config {cfg} keeping the hidden/K-V mix "
-            f"({sum(s_lens)} cached tokens) per step; tokens/s = sampled requests / time")
-    line = {"impl": "reference", "metric": METRIC, "value": round(value, 3), "unit": UNIT,
-            "n_gpus": args.gpus, "steps": args.steps, "warmup": min(args.warmup, 1),
-            "ms_per_step": round(sec * 1e3, 3), "higher_is_better": True,
-            "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic",
-            "config": {"workload": f"config {cfg}: {shape.name} layer, bounded sample", "seed": seed},
-            "cpu_baseline": {"value": round(value, 3), "unit": UNIT, "cores": torch.get_num_threads(),
-                             "host_cpus": os.cpu_count(), "kind": "port", "sample": desc},
-            "e2e": {"value": round(value, 3), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    B = len(lens)
+    K, W = args.steps, max(1, min(args.warmup, 3))
+    gpu = None
+    why = None
+    if torch.cuda.is_available() and shape.dtype != torch.bfloat16:
+        from oracle.literal_chain_gpu import LiteralChain
+        chain, why = LiteralChain.create()
+    else:
+        chain = None
+        why = "no CUDA device" if not torch.cuda.is_available() else "the reference's extension has no bf16 dispatch"
+    if chain is not None:
+        torch.cuda.set_device(local_rank)
+        dev = torch.device("cuda", local_rank)
+        w = make_decode_workload(shape, lens, hid, seed, dev, with_shared_cache=True)
+        m = w.meta
+        hd = w.heads * shape.head_dim
+        w_kv, b_kv = w.qkv_weight[hd:], w.qkv_bias[hd:]
+
+        def step(hidden_states, query, meta):
+            return chain.hybrid_decode_layer(hidden_states, query, w_kv, b_kv, w.kv_cache, w.shared_cache, meta, w.scale)
+        for _ in range(W):
+            step(w.hidden_states, w.query, m)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(K):
+            step(w.hidden_states, w.query, m)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / K
+        # end to end: the step's inputs as the reference's model runner ships them every step
+        # (layer input, query and the index tensors of the batch), result copied back
+        names = ["slot_mapping", "slot_mapping_shared", "hidden_cache_use_tot", "kv_cache_use_tot",
+                 "hidden_cache_use_input", "hidden_cache_store_tot", "hidden_holder_upd", "hidden_holder_pull",
+                 "block_tables", "seq_lens_tensor"]
+        host = {n: getattr(m, n).cpu().pin_memory() for n in names}
+        host["hidden_states"] = w.hidden_states.cpu().pin_memory()
+        host["query"] = w.query.cpu().pin_memory()
+        devbuf = {n: torch.empty_like(v, device=dev) for n, v in host.items()}
+        from dataclasses import replace
+        m_dev = replace(m, **{n: devbuf[n] for n in names})
+        host_out = torch.empty(tuple(w.query.shape), dtype=shape.dtype).pin_memory()
+
+        def e2e_step():
+            for n, v in host.items():
+                devbuf[n].copy_(v, non_blocking=True)
+            out = step(devbuf["hidden_states"], devbuf["query"], m_dev)
+            host_out.copy_(out, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+        for _ in range(2):
+            e2e_step()
+        t0 = time.perf_counter()
+        for _ in range(K):
+            e2e_step()
+        e2e_s = (time.perf_counter() - t0) / K
+        n_hid_tok, n_kv = int(m.slot_mapping_shared.numel()), int(m.kv_cache_use_tot.numel())
+        gpu = {"ms": ms, "e2e_s": e2e_s,
+               "h2d": sum(v.numel() * v.element_size() for v in host.values()),
+               "d2h": host_out.numel() * host_out.element_size(),
+               "attention": chain.attention_name,
+               "notes": ([] if chain.inside_mixed_envelope(m) else
+                         [f"mixed_kv_to_cache runs unmodified: with {n_hid_tok} cached hidden tokens and {n_kv} K/V "
+                          "requests its hidden-token index (blockIdx.x % (2 * n_kv), mixed_cache.cu:88) aliases, so it "
+                          "writes fewer distinct rows than intended (less traffic than the intended op; its output "
+                          "is not checked here)"]) +
+                        ["K/V-cached requests attend over the shared cache through their private ids, as the "
+                         "reference does (aptserve_flash_attn.py:464-473)"]}
+        del w
+        torch.cuda.empty_cache()
+
+    # the CPU restatement on a bounded sample of the same batch
+    hd_full = shape.num_heads * shape.head_dim
+    budget = min(args.cpu_flops, 6e13 / max(1, K)) if gpu is not None else min(args.cpu_flops, 2.4e14 / max(1, K))
+    sample = cpu_sample_requests(lens, hid, budget, shape.hidden, hd_full)
+    s_lens, s_hid = [lens[r] for r in sample], [hid[r] for r in sample]
+    wc = make_decode_workload(shape, s_lens, s_hid, seed, "cpu")
+    cpu_steps = K if gpu is None else min(K, 2)
+    sec = run_cpu_port(wc, list(range(len(sample))), cpu_steps, min(args.warmup, 1) if gpu is None else 0)
+    cpu_value = len(sample) / sec
+    cpu_block = {"value": round(cpu_value, 3), "unit": UNIT, "cores": torch.get_num_threads(),
+                 "host_cpus": os.cpu_count(), "kind": "port",
+                 "sample": f"{len(sample)} of {B} requests of config {cfg} keeping the hidden/K-V mix "
+                           f"({sum(s_lens)} cached tokens), {cpu_steps} steps of {sec:.2f} s; "
+                           "tokens/s = sampled requests / time"}
+    base = {"impl": "reference", "metric": METRIC, "unit": UNIT, "n_gpus": args.gpus, "steps": K,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "data": "synthetic",
+            "cpu_baseline": cpu_block}
+    wl = (f"config {cfg}: {shape.name} layer ({shape.num_heads} heads x {shape.head_dim}, hidden {shape.hidden}), "
+          f"{B} decode requests, {sum(hid)} hidden-cached, seed {seed}")
+    if gpu is not None:
+        line = dict(base, value=round(B / (gpu["ms"] * 1e-3), 2), warmup=W, ms_per_step=round(gpu["ms"], 4),
+                    dtype=dtype_name(shape.dtype),
+                    config={"workload": wl, "seed": seed, "parallelism": "single GPU (rank 0)",
+                            "step": "hidden_to_cache + zero-filled hidden_holder + cache_to_hidden + kv_only projection "
+                                    "+ mixed_kv_to_cache + paged decode attention over the shared cache"},
+                    reference_kernels={"kind": "reference",
+                                       "mixed_cache_ops": "the reference's mixed_cache.cu compiled unmodified for sm_100a (oracle/_ref)",
+                                       "projection": "torch.nn.functional.linear (cuBLAS)",
+                                       "attention": gpu["attention"], "notes": gpu["notes"]},
+                    e2e={"value": round(B / gpu["e2e_s"], 2), "unit": UNIT, "h2d_bytes_per_step": gpu["h2d"],
+                         "d2h_bytes_per_step": gpu["d2h"], "ms_per_step": round(gpu["e2e_s"] * 1e3, 4)})
+    else:
+        line = dict(base, value=round(cpu_value, 3), warmup=min(args.warmup, 1), ms_per_step=round(sec * 1e3, 3),
+                    dtype="f32",
+                    config={"workload": wl + ", bounded sample on the host cores", "seed": seed},
+                    reference_kernels={"kind": "port", "gpu_chain_unavailable": why},
+                    e2e={"value": round(cpu_value, 3), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0})
     print(json.dumps(line))
 
 
@@ -588,10 +899,10 @@ def main():
     ap.add_argument("--cpu-flops", type=float, default=2e13,
                     help="re-projection FLOPs of the host-core baseline's sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="headline measurement only (no sub-batch, configuration 3/4/5 blocks)")
     args = ap.parse_args()
     if args.impl == "reference":
-        # bounded: the host cores do ~2 TFLOP/s, so K steps of the sample stay near two minutes
-        args.cpu_flops = min(args.cpu_flops, 2.4e14 / max(1, args.steps))
         run_reference(args)
     else:
         run_ours(args)

@@ -21,7 +21,13 @@
  *  - nothing is allocated or freed for the caller and no pointer is retained
  *    after return;
  *  - the return value is an aps_status; no C++ exception crosses the boundary;
- *    aps_last_error() gives a human-readable message for the calling thread.
+ *    aps_last_error() gives a human-readable message for the calling thread;
+ *  - ONE calling thread per process, one call at a time (the reference's worker is
+ *    single-threaded Python, one process per GPU): per-device launch geometry, the
+ *    table of encoded tensor maps, the address of the built-in scratch and the
+ *    profile-event hook are plain process- or thread-local statics without locks.
+ *    Different processes on different GPUs are independent;
+ *  - the library reads no environment variable.
  */
 #ifndef APTSERVE_B200_H_
 #define APTSERVE_B200_H_
@@ -189,9 +195,11 @@ int aps_paged_decode_attention(void* out, const void* query, const void* key_cac
  *  - A batch whose scratch need (aps_attention_workspace_bytes of its shape)
  *    exceeds 32 MiB is rejected with APS_ERR_WORKSPACE; e.g. 64 requests x 2048
  *    tokens at 40 heads x 128 need about 23 MiB and fit, 256 such requests do not.
- *  - The first call on each device looks up the array's device address
- *    (cudaGetSymbolAddress, with that device current); make that first call
- *    before any stream capture begins.
+ *  - Every call looks up the array's device address (cudaGetSymbolAddress, with
+ *    the calling thread's device current) and keeps nothing between calls, so a host
+ *    that tears its CUDA context down and builds a new one is served correctly.
+ *    The very first lookup on a device loads the library's device image: make a
+ *    first call on each device before any stream capture begins.
  *  - All calls share the one array.  Everything a call reads from it is written
  *    earlier in the same call (its first kernel resets the work counter, the list
  *    sizes and the status word), so stale contents are harmless; but two calls
@@ -224,6 +232,9 @@ int aps_paged_decode_attention_static(void* out, const void* query, const void* 
  * num_hidden_rows is the number of addressable rows of hidden_cache
  * (2*NB*BS for the reference layout).  fp16 / bf16 with head_size 128 use the
  * tcgen05 path; other supported combinations use a CUDA-core re-projection.
+ * key_cache / value_cache may both be NULL for a batch without K/V-cached requests;
+ * if such a batch does hold K/V-cached requests their output rows are zero and the
+ * status word (aps_attention_status) reads 8.
  */
 int aps_hybrid_decode_attention(void* out, const void* query, const void* key_cache,
                                 const void* value_cache, const void* hidden_cache,
@@ -256,11 +267,61 @@ int aps_kv_reprojection(void* kv, const void* x, const int32_t* block_ids, int64
                         int* status_word, void* stream);
 
 /*
- * Reads the status word the attention kernels keep in `workspace` (0 = fine,
- * non-zero = a bounded device-side wait ran out in the last call that used this
- * workspace).  Synchronises `stream`.  Meant for tests and debugging.
+ * One decode layer-step in one call: everything between the projections and o_proj
+ * of OPTAttention.forward's decode branch (opt.py:99-134 with fa.py:331-387,
+ * 449-475).  Enqueues, in this order,
+ *   1. the new token's cache writes, addressed from block_tables / seq_lens /
+ *      cache_type (position seq_lens[r] - 1): hidden_states[r] -> hidden cache row for
+ *      hidden-cached requests (hidden_to_cache, opt.py:108-109), new_key[r] /
+ *      new_value[r] -> K/V planes for K/V-cached requests (the private-cache half of
+ *      mixed_kv_to_cache, fa.py:363-373, or reshape_and_cache_flash, fa.py:338-345);
+ *   2. aps_hybrid_decode_attention over the batch.
+ * hidden_states [B, hidden_size], new_key / new_value [B, H*D] (rows of the other
+ * cache type are ignored; a NULL pointer skips that kind of write), every pointer
+ * and row 16-byte aligned.  All other arguments as in aps_hybrid_decode_attention.
+ */
+int aps_decode_layer_step(void* out, const void* query, const void* hidden_states,
+                          const void* new_key, const void* new_value, void* key_cache,
+                          void* value_cache, void* hidden_cache, const void* w_k,
+                          const void* b_k, const void* w_v, const void* b_v,
+                          const int32_t* block_tables, const int32_t* seq_lens,
+                          const int32_t* cache_type, int batch, int max_blocks_per_seq,
+                          int num_heads, int head_size, int hidden_size, int block_size,
+                          int64_t query_stride, int64_t out_stride, int64_t hidden_states_stride,
+                          int64_t new_key_stride, int64_t new_value_stride, int64_t block_stride,
+                          int64_t hidden_row_stride, int64_t num_hidden_rows, int64_t w_stride,
+                          float scale, void* workspace, size_t workspace_bytes, int dtype,
+                          void* stream);
+
+/*
+ * Reads the status word the attention kernels keep in `workspace` for the last call
+ * that used it.  0 = fine.  1..7 = a bounded device-side wait of the re-projection
+ * kernel ran out (the kernel returned early; the call's whole output was filled with
+ * NaN).  8 = the batch held K/V-cached requests but no K/V cache was passed (their
+ * output rows are zero).  Synchronises `stream`: call it where a synchronisation is
+ * cheap, e.g. once per engine step next to the sampler's device-to-host copy.
  */
 int aps_attention_status(const void* workspace, int* host_status, void* stream);
+
+/*
+ * Status of the bulk-copy cache writes on the current device: 0, or 1 once a bounded
+ * wait on a bulk load ran out (the launch then stopped copying).  Synchronises `stream`.
+ */
+int aps_cache_ops_status(int* host_status, void* stream);
+
+/*
+ * Test aid for the status handling (no counterpart in the reference).  `workspace` must
+ * have been used by an attention call of the given shape.  One thread waits on an
+ * mbarrier that nothing arrives on, gives up after budget_cycles clock cycles (1 .. 1e8,
+ * i.e. at most ~0.1 s) and records code 7 in the workspace's status word, exactly as the
+ * bounded waits of the re-projection kernel do; then the attention's combine step runs
+ * again over the workspace and, seeing the code, fills `out` [batch, H*D] with NaN.
+ * Nothing hangs or faults and the context stays usable.
+ */
+int aps_selftest_bounded_wait(void* workspace, size_t workspace_bytes, long long budget_cycles,
+                              void* out, int batch, int max_blocks_per_seq, int num_heads,
+                              int head_size, int block_size, int64_t out_stride, int dtype,
+                              void* stream);
 
 /* ------------------------------------------------------------------------ */
 /* Index tensors                                                             */
@@ -281,9 +342,13 @@ int aps_attention_status(const void* workspace, int* host_status, void* stream);
  *   slot_mapping [N_tot], slot_mapping_shared [N_h], hidden_cache_use_tot [N_h],
  *   kv_cache_use_tot [n_kv], hidden_holder_upd [B], hidden_holder_pull [N_tot - B],
  *   hidden_cache_store_tot [n_h], hidden_cache_use_input [n_h].
- * num_tot_tokens / num_hidden_tokens are the capacities of the N_tot / N_h tensors (the
- * host knows them from the sequence lengths); nothing is written past them.  counts
- * (device int64[4], may be NULL) receives N_tot, N_h, n_kv, n_h as computed on the device.
+ * num_tot_tokens / num_hidden_tokens are the caller's N_tot / N_h (the host knows them from
+ * the sequence lengths; a length below 1 counts as 1); n_kv = N_tot - N_h and n_h = B - n_kv
+ * follow.  An output that is empty for these counts may be NULL.  The kernels recompute the
+ * four counts from the device-side seq_lens / cache_type: if they differ from the caller's,
+ * NOTHING is written (the outputs keep their previous contents), and no store ever goes past
+ * a tensor's capacity.  counts (device int64[4], may be NULL) receives N_tot, N_h, n_kv, n_h
+ * as computed on the device, so a caller can detect the mismatch.
  * scratch: aps_decode_metadata_scratch_bytes(B) bytes of device memory.
  */
 size_t aps_decode_metadata_scratch_bytes(int batch);
@@ -300,7 +365,7 @@ int aps_expand_decode_metadata(const int32_t* block_tables, const int32_t* block
 /*
  * Timing hook for benchmarks (no counterpart in the reference, whose kernels are
  * timed with commented-out torch.cuda.synchronize() calls, fa.py:374-387):
- * while set, the attention calls of THIS THREAD record `start_event` just before
+ * while set (a thread-local, unsynchronised hook), the attention calls of THIS THREAD record `start_event` just before
  * and `stop_event` just after the launch of the K/V streaming kernel (which = 0)
  * or of the re-projection kernel (which = 1), on the stream of the call.  Events
  * are cudaEvent_t handles owned by the caller; pass NULL, NULL to switch off.

@@ -21,7 +21,9 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 OUT_DIR = HERE / "_ref"
-REFERENCE_ROOT = Path(os.environ.get("APTSERVE_REFERENCE", "/root/reference"))
+# where the reference checkout lies: $APTSERVE_REFERENCE, else a directory named "reference"
+# beside this repository
+REFERENCE_ROOT = Path(os.environ.get("APTSERVE_REFERENCE") or HERE.parent.parent / "reference")
 SOURCE = REFERENCE_ROOT / "additional_designs" / "mixed_cache_kernels" / "mixed_cache.cu"
 MODULE = "mixed_cache_ops"
 

@@ -99,3 +99,62 @@ def test_backend_static_api():
         FlashAttentionImpl(4, 100, 0.1, 4, None, None, "auto")
     with pytest.raises(ValueError):
         FlashAttentionImpl(4, 128, 0.1, 4, None, 1024, "auto")
+
+
+def test_advertised_head_sizes_are_the_ones_the_kernels_take():
+    """Every head size the backend advertises passes the decode attention's argument check for
+    fp16, and the sizes of the reference's list that the kernels do not take are refused."""
+    from apt_serve_b200.attention import FlashAttentionBackend
+    lib = N.lib()
+    buf = (ctypes.c_char * 8192)()
+    p = (ctypes.addressof(buf) + 255) // 256 * 256
+    sizes = FlashAttentionBackend.get_supported_head_sizes()
+    assert sizes == [32, 64, 128, 256]
+    for d in (32, 64, 96, 128, 160, 192, 224, 256):
+        # batch 1 with a far too small workspace: a supported size gets as far as the workspace check
+        st = lib.aps_paged_decode_attention(p, p, p, p, p, p, 1, 4, 2, d, 16, 2 * d, 2 * d, 32 * d, 1.0,
+                                            p, 16, 1, 0)
+        assert st == (N.APS_ERR_WORKSPACE if d in sizes else N.APS_ERR_UNSUPPORTED), d
+
+
+def test_absorbed_variant_falls_back_for_shapes_it_is_not_built_for():
+    from apt_serve_b200.attention import absorbed_supported
+    from apt_serve_b200.layers import OPTAttention
+    assert absorbed_supported(40, 5120, torch.float16)          # OPT-13B
+    assert absorbed_supported(72, 9216, torch.bfloat16)         # OPT-66B, padded to 80 heads
+    assert absorbed_supported(9, 9216, torch.bfloat16)          # OPT-66B at tp = 8
+    assert not absorbed_supported(56, 7168, torch.float16)      # OPT-30B: 56 heads pad to 64
+    assert not absorbed_supported(12, 768, torch.float32)       # fp32
+    assert not absorbed_supported(12, 768, torch.float16)       # hidden size not a multiple of 512
+    e, h = 7168, 56
+    z = torch.zeros
+    layer = OPTAttention(e, h, z(3 * e, 8), None, z(8, e), None, fused="absorbed")
+    assert not layer.use_absorbed(torch.float16)
+    layer = OPTAttention(5120, 40, z(3 * 5120, 8), None, z(8, 5120), None, fused="absorbed")
+    assert layer.use_absorbed(torch.float16) and not layer.use_absorbed(torch.float32)
+    assert not OPTAttention(5120, 40, z(3 * 5120, 8), None, z(8, 5120), None, fused=True).use_absorbed(torch.float16)
+
+
+def test_decode_layer_step_argument_checks():
+    lib = N.lib()
+    buf = (ctypes.c_char * 8192)()
+    p = (ctypes.addressof(buf) + 255) // 256 * 256
+    args = dict(batch=1, max_blocks=4, heads=2, d=128, e=256, bs=16)
+
+    def call(cache_type=p, new_key=p, new_value=p, key_cache=p, value_cache=p, hs_stride=256):
+        return lib.aps_decode_layer_step(p, p, p, new_key, new_value, key_cache, value_cache, p, p, 0, p, 0,
+                                         p, p, cache_type, 1, 4, 2, 128, 256, 16, 256, 256, hs_stride, 256, 256,
+                                         16 * 256, 256, 64, 256, 1.0, p, 16, 1, 0)
+    assert call() == N.APS_ERR_WORKSPACE               # everything else is in order
+    assert call(cache_type=0) == N.APS_ERR_WORKSPACE   # (the workspace check comes first)
+    big = 1 << 30
+
+    def call_ws(**kw):
+        a = dict(cache_type=p, new_key=p, new_value=p, key_cache=p, value_cache=p, hs_stride=256)
+        a.update(kw)
+        return lib.aps_decode_layer_step(p, p, p, a["new_key"], a["new_value"], a["key_cache"], a["value_cache"],
+                                         p, p, 0, p, 0, p, p, a["cache_type"], 1, 4, 2, 128, 256, 16, 256, 256,
+                                         a["hs_stride"], 256, 256, 16 * 256, 256, 64, 256, 1.0, p, big, 1, 0)
+    assert call_ws(cache_type=0) == N.APS_ERR_NULL_POINTER
+    assert call_ws(value_cache=0) == N.APS_ERR_NULL_POINTER      # one cache plane without the other
+    assert call_ws(hs_stride=8) == N.APS_ERR_SHAPE

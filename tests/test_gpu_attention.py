@@ -166,7 +166,12 @@ def test_hybrid_full_config2_subset_oracle_and_permutation_invariance():
     rng = np.random.default_rng(0)
     hid = [r for r, h in enumerate(w.use_hidden) if h]
     kv = [r for r, h in enumerate(w.use_hidden) if not h]
-    pick = sorted(rng.choice(hid, 3, replace=False).tolist() + rng.choice(kv, 3, replace=False).tolist())
+    # always the longest and the shortest request of each cache type, plus a seeded draw
+    by_len = lambda rows: sorted(rows, key=lambda r: w.seq_lens[r])
+    pick = {by_len(hid)[0], by_len(hid)[-1], by_len(kv)[0], by_len(kv)[-1]}
+    pick |= set(rng.choice(hid, 2, replace=False).tolist()) | set(rng.choice(kv, 2, replace=False).tolist())
+    pick = sorted(pick)
+    assert max(w.seq_lens[r] for r in pick if w.use_hidden[r]) >= 1500
     cpu = w.cpu()
     ref = oracle_out(cpu, requests=pick)
     assert_close(out[pick], ref[pick], "config 2 subset")
@@ -233,12 +238,109 @@ def test_hybrid_cuda_core_reprojection_shapes(dtype, heads, head_dim):
     assert_close(out, ref, f"CUDA-core re-projection {dtype} D{head_dim}", tol, tol)
 
 
-def test_cuda_core_and_tensor_core_reprojection_agree(monkeypatch):
+def test_cuda_core_and_tensor_core_reprojection_agree():
+    """The same fp16 values through the tcgen05 kernel (fp16 tensors) and through the
+    CUDA-core kernel (the same values held as fp32 tensors)."""
     w = small_workload(heads=2, head_dim=128, lens=(70, 300, 129), hidden=(True, True, False)).to("cuda")
     tensor = gpu_hybrid(w).clone()
-    monkeypatch.setenv("APS_FORCE_SIMT", "1")
-    simt = gpu_hybrid(w)
+    wk, bk, wv, bv = (t.float() for t in w.kv_weights())
+    simt = A.hybrid_decode_attention(w.query.float(), w.kv_cache.float(), w.hidden_cache.float(), wk, bk,
+                                     wv, bv, w.meta.private_block_tables, w.meta.seq_lens_tensor,
+                                     w.meta.cache_type, w.scale)
     assert_close(simt, tensor.float(), "CUDA-core vs tensor-core path", 5e-3, 5e-3)
+
+
+# --------------------------------------------------------------------------- #
+# device status word
+# --------------------------------------------------------------------------- #
+def test_kv_requests_without_kv_cache_set_the_status_and_give_zero_rows():
+    """A batch with K/V-cached requests but no K/V cache: the call succeeds on the host
+    (it cannot see the cache types), the status word reads 8, the K/V requests' rows are
+    zero (no stale partials are merged) and the hidden requests' rows are right."""
+    w = small_workload(heads=2, head_dim=128, lens=(40, 9, 150, 64), hidden=(True, False, True, False))
+    ref = oracle_out(w)
+    dev = w.to("cuda")
+    gpu_hybrid(dev)   # leaves valid partials of every request in the workspace
+    wk, bk, wv, bv = dev.kv_weights()
+    out = A.hybrid_decode_attention(dev.query, None, dev.hidden_cache, wk, bk, wv, bv,
+                                    dev.meta.private_block_tables, dev.meta.seq_lens_tensor,
+                                    dev.meta.cache_type, dev.scale, num_heads=2, head_size=128)
+    ws = A.attention_workspace(out.device, 1, 1, 16, 1, 1)
+    assert A.attention_status(ws) == 8
+    with pytest.raises(RuntimeError, match="status 8"):
+        A.raise_on_device_status(ws)
+    assert_close(out[[0, 2]], ref[[0, 2]], "hidden requests without a K/V cache")
+    assert float(out[[1, 3]].abs().max()) == 0.0
+    assert A.attention_status(A.attention_workspace(out.device, 1, 1, 16, 1, 1)) == 8
+    gpu_hybrid(dev)   # the next complete call resets the word
+    A.raise_on_device_status(ws)
+
+
+def test_bounded_wait_that_runs_out_marks_the_output():
+    """A wait nobody satisfies gives up after its clock budget and leaves code 7; the
+    combine step then writes NaN instead of numbers; the next call works as before."""
+    from apt_serve_b200 import _native as N
+    w = small_workload(heads=2, head_dim=128, lens=(40, 9, 150), hidden=(True, False, True)).to("cuda")
+    good = gpu_hybrid(w).clone()
+    ws = A.attention_workspace(good.device, 1, 1, 16, 1, 1)
+    out = torch.zeros_like(good)
+    bt = w.meta.private_block_tables
+    N.check(N.lib().aps_selftest_bounded_wait(N.ptr(ws), ws.numel(), 200000, N.ptr(out), 3, bt.shape[1], 2, 128,
+                                              16, out.stride(0), N.dtype_enum(out), N.current_stream(out.device)))
+    assert A.attention_status(ws) == 7
+    assert torch.isnan(out.float()).all()
+    with pytest.raises(RuntimeError, match="status 7"):
+        A.raise_on_device_status(ws)
+    assert torch.equal(gpu_hybrid(w), good)
+
+
+# --------------------------------------------------------------------------- #
+# the layer-step in one call
+# --------------------------------------------------------------------------- #
+@pytest.mark.parametrize("case", ["fp16 aliased", "bf16 tensor-parallel slice", "fp32 config 1"])
+def test_decode_layer_step_equals_separate_ops(case):
+    """aps_decode_layer_step (new-token writes addressed from the block tables + attention)
+    against the three separate calls fed from the index tensors: same cache bits, same
+    output bits, and both within tolerance of the oracle's layer-step."""
+    from apt_serve_b200 import mixed_cache_ops, ops
+    if case == "fp16 aliased":
+        w = small_workload(heads=2, head_dim=128, lens=(5, 40, 17, 129, 300, 16, 128, 1),
+                           hidden=(True, False, True, False, True, False, True, True), device="cuda")
+        tol = 2e-2
+    elif case == "bf16 tensor-parallel slice":
+        from apt_serve_b200.workloads import OPT_66B
+        w = make_decode_workload(OPT_66B, [33, 200, 16, 310], [True, False, False, True], seed=11,
+                                 device="cuda", tp_rank=3, tp_size=8)
+        tol = 2e-2
+    else:
+        w = make_config_workload(1, device="cuda", kv_from_projection=True)
+        tol = 1e-3
+    cpu = w.cpu()
+    ref = O.decode_layer_step(cpu.hidden_states, cpu.query, cpu.new_key, cpu.new_value, cpu.kv_cache,
+                              cpu.hidden_cache, *cpu.kv_weights(), cpu.meta, cpu.scale)
+    m, h, d = w.meta, w.heads, w.shape.head_dim
+    alias = w.hidden_cache.data_ptr() == w.kv_cache.data_ptr()
+    kv_a, kv_b = w.kv_cache.clone(), w.kv_cache.clone()
+    hid_a = kv_a if alias else w.hidden_cache.clone()
+    hid_b = kv_b if alias else w.hidden_cache.clone()
+    wk, bk, wv, bv = w.kv_weights()
+    # separate ops
+    rows = m.kv_request_rows
+    ops.reshape_and_cache_flash(w.new_key[rows].view(-1, h, d), w.new_value[rows].view(-1, h, d),
+                                kv_a[0], kv_a[1], m.slot_mapping[m.kv_cache_use_tot])
+    mixed_cache_ops.hidden_to_cache(w.hidden_states, hid_a, m.slot_mapping, m.hidden_cache_use_input,
+                                    m.hidden_cache_store_tot)
+    out_a = A.hybrid_decode_attention(w.query, kv_a, hid_a, wk, bk, wv, bv, m.private_block_tables,
+                                      m.seq_lens_tensor, m.cache_type, w.scale).clone()
+    # one call
+    out_b = A.decode_layer_step(w.query, w.hidden_states, w.new_key, w.new_value, kv_b, hid_b, wk, bk,
+                                wv, bv, m.private_block_tables, m.seq_lens_tensor, m.cache_type, w.scale)
+    A.raise_on_device_status()
+    assert torch.equal(kv_a.view(torch.uint8), kv_b.view(torch.uint8))
+    assert torch.equal(hid_a.view(torch.uint8), hid_b.view(torch.uint8))
+    assert torch.equal(kv_b.cpu().view(torch.uint8), cpu.kv_cache.view(torch.uint8))
+    assert torch.equal(out_a, out_b)
+    assert_close(out_b, ref, f"decode_layer_step {case}", tol, tol)
 
 
 # --------------------------------------------------------------------------- #
