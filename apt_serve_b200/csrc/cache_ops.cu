@@ -13,7 +13,7 @@
 //          while this row is stored.  One instruction per 10 KB instead of one load/store
 //          pair per 16 bytes.  What a CTA spends per row is a chain of round trips counted
 //          in SM cycles, so the number of CTAs per SM is what matters at the ~1 GHz SM clock
-//          the power cap leaves inside a decode step: two buffers of one row each let eleven
+//          the power cap leaves inside a decode step: two buffers of one row each let ten
 //          CTAs share an SM for 10 KB rows (measured inside the loaded step on OPT-13B
 //          prefill rows: 5.4 TB/s read + write; deeper rings with fewer CTAs 3.0 - 4.0 TB/s,
 //          the vector kernels 3.9 TB/s).
