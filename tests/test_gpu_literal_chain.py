@@ -65,8 +65,11 @@ def block_size_for(chain, want=16):
 
 def test_kv_only_batch_against_third_party_paged_attention(chain):
     """aptserve_flash_attn.py:452-461: a K/V-only decode batch over the private cache."""
+    # one (dtype, head size) only: the third-party kernel is compiled for this GPU at its first
+    # call per instantiation, which takes about a minute each; the other dtypes and head sizes
+    # of the K/V path are checked against the CPU oracle in test_gpu_attention.py
     bs = block_size_for(chain)
-    for dtype, heads, d in ((torch.float16, 4, 128), (torch.bfloat16, 3, 128), (torch.float16, 5, 64)):
+    for dtype, heads, d in ((torch.float16, 4, 128),):
         shape = LayerShape("t", heads, d, heads * d, dtype, block_size=bs)
         lens = [1, 15, 16, 17, 127, 128, 129, 300, 1000, 2048]
         w = make_decode_workload(shape, lens, [False] * len(lens), seed=5, device="cuda")
