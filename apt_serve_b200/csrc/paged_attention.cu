@@ -532,21 +532,34 @@ combine_kernel(const int* __restrict__ plan, const int* __restrict__ part_offset
     for (int d = lane; d < head_size; d += 32) dst[d] = Elem<T>::from_float(__int_as_float(0x7fc00000));
     return;
   }
+  // the lanes share the request's partials for the maximum and the denominator (butterfly
+  // reductions: the same order every time), then every lane owns four head elements and walks
+  // the partials in chunk order with independent 16-byte loads
   float mx = -INFINITY;
-  for (int p = p0; p < p1; ++p) mx = fmaxf(mx, part_ml[((int64_t)p * heads + h) * 2]);
+  for (int p = p0 + lane; p < p1; p += 32) mx = fmaxf(mx, part_ml[((int64_t)p * heads + h) * 2]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(kFull, mx, o));
   float denom = 0.f;
-  for (int p = p0; p < p1; ++p) {
+  for (int p = p0 + lane; p < p1; p += 32) {
     const float2 ml = *reinterpret_cast<const float2*>(part_ml + ((int64_t)p * heads + h) * 2);
     denom += exp2f(ml.x - mx) * ml.y;
   }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) denom += __shfl_xor_sync(kFull, denom, o);
   const float inv = (p1 > p0 && denom > 0.f) ? 1.f / denom : 0.f;
-  for (int d = lane; d < head_size; d += 32) {
-    float a = 0.f;
+  for (int d = lane * 4; d < head_size; d += 128) {
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
     for (int p = p0; p < p1; ++p) {
       const int64_t slot = (int64_t)p * heads + h;
-      a = fmaf(exp2f(part_ml[slot * 2] - mx), part_acc[slot * head_size + d], a);
+      const float w = exp2f(part_ml[slot * 2] - mx);
+      const float4 v = *reinterpret_cast<const float4*>(part_acc + slot * head_size + d);
+      a.x = fmaf(w, v.x, a.x); a.y = fmaf(w, v.y, a.y); a.z = fmaf(w, v.z, a.z); a.w = fmaf(w, v.w, a.w);
     }
-    dst[d] = Elem<T>::from_float(a * inv);
+    dst[d] = Elem<T>::from_float(a.x * inv);
+    dst[d + 1] = Elem<T>::from_float(a.y * inv);
+    dst[d + 2] = Elem<T>::from_float(a.z * inv);
+    dst[d + 3] = Elem<T>::from_float(a.w * inv);
   }
 }
 

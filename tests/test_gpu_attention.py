@@ -423,6 +423,40 @@ def test_opt_attention_prefill_fused_write_matches_literal():
     assert_close(outs[0], outs[1].float(), "prefill output", 1e-3, 1e-3)
 
 
+def test_decode_layer_step_replays_from_a_cuda_graph():
+    """The layer-step enqueues kernels and nothing else (no allocation, no synchronisation, no
+    host read of device data), so it can be captured in a CUDA graph -- the reference itself
+    cannot (it must run with --enforce-eager).  A captured step is replayed on new inputs
+    written into the captured buffers and compared, bit for bit, with an eager call."""
+    w = small_workload(heads=2, head_dim=128, lens=(5, 40, 17, 129, 300, 16, 128, 1),
+                       hidden=(True, False, True, False, True, False, True, True), device="cuda")
+    m = w.meta
+    wk, bk, wv, bv = w.kv_weights()
+    ws = A.attention_workspace(w.query.device, len(w.seq_lens), m.private_block_tables.shape[1], 16, 2, 128)
+    kv_graph, kv_eager = w.kv_cache.clone(), w.kv_cache.clone()
+    q, hs, nk, nv = w.query.clone(), w.hidden_states.clone(), w.new_key.clone(), w.new_value.clone()
+    out_graph = torch.empty_like(q)
+
+    def step(kv, out):
+        return A.decode_layer_step(q, hs, nk, nv, kv, kv, wk, bk, wv, bv, m.private_block_tables,
+                                   m.seq_lens_tensor, m.cache_type, w.scale, out=out, workspace=ws)
+    step(w.kv_cache.clone(), torch.empty_like(q))       # first call: kernel attributes, tensor maps
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        step(kv_graph, out_graph)
+    for seed in (1, 2):
+        gen = torch.Generator(device="cuda").manual_seed(seed)
+        for t in (q, hs, nk, nv):
+            t.copy_(torch.randn(t.shape, device="cuda", generator=gen).to(t.dtype))
+        g.replay()
+        ref = step(kv_eager, torch.empty_like(q))
+        torch.cuda.synchronize()
+        A.raise_on_device_status(ws)
+        assert torch.equal(out_graph, ref)
+        assert torch.equal(kv_graph.view(torch.uint8), kv_eager.view(torch.uint8))
+
+
 # --------------------------------------------------------------------------- #
 # seeded sweep over ragged batch compositions (tile packing, segments, edges)
 # --------------------------------------------------------------------------- #
