@@ -17,7 +17,7 @@ CSRC = PKG / "csrc"
 LIB_DIR = PKG / "lib"
 LIB_PATH = LIB_DIR / "libaptserve_b200.so"
 SOURCES = ["c_api.cu", "cache_ops.cu", "paged_attention.cu", "hybrid_attention.cu", "hidden_simt.cu", "metadata_ops.cu",
-           "tp_comm.cu", "absorbed_attention.cu", "decode_step.cu"]
+           "tp_comm.cu", "absorbed_attention.cu", "decode_step.cu", "tensor_maps.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-cudart", "shared"]
 

@@ -47,6 +47,7 @@
 // and the CTA drains, frees its tensor memory and returns.
 
 #include "attention_common.cuh"
+#include "tensor_maps.cuh"
 
 #include <cuda.h>
 #include <stdlib.h>
@@ -742,58 +743,16 @@ __global__ void bounded_wait_selftest_kernel(int* status, long long budget, int 
 }
 
 // ---- host side -----------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                  CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn == nullptr) {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(sym);
-  }
-  return fn;
-}
-
 // 2-D row-major matrix [rows, cols] of 2-byte elements, box [box_rows, 64 cols], 128-byte
-// swizzle.  A tensor map is a pure function of (base, dtype, shape, stride, box): the encoded
-// maps are kept in a small per-thread table, so a layer that is called every step with the
-// same cache and weights encodes its three maps once.
-struct MapKey {
-  const void* base; int dtype; uint64_t cols, rows, stride; uint32_t box_rows;
-  bool operator==(const MapKey& o) const {
-    return base == o.base && dtype == o.dtype && cols == o.cols && rows == o.rows && stride == o.stride &&
-           box_rows == o.box_rows;
-  }
-};
-struct MapSlot { MapKey key; CUtensorMap map; bool used; };
-constexpr int kMapSlots = 32;
-
+// swizzle; encoded once per distinct (pointer, shape, stride, box) and kept (tensor_maps.cu).
 int make_map(CUtensorMap* map, const void* base, int dtype, uint64_t cols, uint64_t rows,
              uint64_t row_stride_elems, uint32_t box_rows, const char* what) {
-  static thread_local MapSlot slots[kMapSlots] = {};
-  static thread_local unsigned next_slot = 0;
-  const MapKey key{base, dtype, cols, rows, row_stride_elems, box_rows};
-  for (int i = 0; i < kMapSlots; ++i)
-    if (slots[i].used && slots[i].key == key) { *map = slots[i].map; return APS_OK; }
-  EncodeTiledFn fn = encode_fn();
-  APS_REQUIRE(fn != nullptr, APS_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-  const CUtensorMapDataType dt = dtype == APS_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {row_stride_elems * 2};
-  cuuint32_t box[2] = {64, box_rows};
-  cuuint32_t elem_strides[2] = {1, 1};
-  CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  APS_REQUIRE(r == CUDA_SUCCESS, APS_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, (int)r);
-  MapSlot& s = slots[next_slot++ % kMapSlots];
-  s.key = key; s.map = *map; s.used = true;
-  return APS_OK;
+  TensorMapSpec spec{};
+  spec.base = base; spec.dtype = dtype; spec.rank = 2;
+  spec.dims[0] = cols; spec.dims[1] = rows;
+  spec.strides_bytes[0] = row_stride_elems * 2;
+  spec.box[0] = 64; spec.box[1] = box_rows;
+  return cached_tensor_map(map, spec, what);
 }
 
 // Work-order group sizes (tile pairs x heads).  4 x 10: of the orders that cost the same cycles

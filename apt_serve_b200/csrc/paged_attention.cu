@@ -5,26 +5,26 @@
 // one query token per request over caches laid out [NB, BS, H, D]
 // (additional_designs/worker/aptserve_cache_engine.py:61-80).
 //
-// Work unit: one warp streams one head of one 128-token chunk, 16 tokens at a time,
-// every lane with 8 independent 16-byte loads of K and 8 of V in flight; the softmax is
-// the online (running max / running sum) form in the log2 domain.  Two kernels:
+// Work unit: one warp streams one head of one 128-token chunk, 16 tokens at a time; the
+// softmax is the online (running max / running sum) form in the log2 domain.  Two kernels:
 //
-//   kv_attention_mma_kernel  (fp16 / bf16, head sizes 64 / 128)  The kernel is
-//       HBM-bound only while the SMs can issue the arithmetic that goes with every byte,
-//       and inside a decode step it runs at the ~1 GHz the board's power cap leaves next to
-//       the re-projection kernel.  So the two small products go to the tensor cores as
-//       mma.sync m16n8k16 with the single query row in row 0 of the A operand: the 16-byte
-//       vectors a lane loads ARE its B fragments (K: two MMAs per vector, no conversion, no
-//       shuffle reduction; V: token pairs are packed with one byte-permute per fragment
-//       register), the score fragment of Q K^T is, rounded to the cache's type, the A
-//       fragment of P V, and the accumulators stay fp32.  About 170 instructions per 16
-//       tokens and warp instead of about 800 on the CUDA cores.
-//   kv_attention_kernel      (fp32; head sizes 32 and 256)  CUDA-core arithmetic: LPR = row
-//       bytes / 16 lanes cover a row with one 16-byte load each, scores are reduced over
-//       those lanes with shuffles.
+//   kv_attention_tma_kernel  (fp16 / bf16, head sizes 64 / 128, cache blocks laid out back to
+//       back as the cache engine allocates them)  The 16-token groups of K and V arrive in
+//       shared memory by tensor copies (cp.async.bulk.tensor, one elected lane per warp, a ring
+//       of three groups per warp with mbarriers) and the two small products run on the tensor
+//       cores as mma.sync m16n8k16 with the single query row in row 0 of the A operand, fed by
+//       ldmatrix: no conversion, no shuffle reduction, no byte permutes, ~100 instructions per
+//       16 tokens and warp.  The kernel is HBM-bound only while the SMs can take in the bytes,
+//       and inside a decode step it runs at the ~1 GHz the board's power cap leaves next to the
+//       re-projection kernel: loads through the load/store unit (16 bytes per lane, whatever the
+//       arithmetic) top out near 29 bytes per SM clock there, tensor copies reach 38.
+//   kv_attention_kernel      (fp32; head sizes 32 and 256; any other block stride)  CUDA-core
+//       arithmetic: LPR = row bytes / 16 lanes cover a row with one 16-byte load each, scores
+//       are reduced over those lanes with shuffles.
 // CTAs are persistent; work is handed out through an atomic counter.
 
 #include "attention_common.cuh"
+#include "tensor_maps.cuh"
 
 namespace aps {
 namespace {
@@ -341,122 +341,211 @@ template <> struct Mma16816<__nv_bfloat16> {
   }
 };
 
-__device__ __forceinline__ uint32_t word_of(const uint4& v, int i) {
-  return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w;
-}
-
-constexpr int kMmaWarps = 4;       // warps per CTA of the tensor-core streaming kernel
-constexpr int kMmaCtasPerSm = 3;
 constexpr int kGroupTokens = 16;   // tokens per softmax step
 
-// K of a 16-token group: two 8-token blocks; lane (g, j) loads, for token g of each block, the
-// 16-byte pieces [c*32 + j*8, +8) of the head's row, c < D/32: four lanes cover 64 contiguous
-// bytes, a warp-wide load 8 rows.  Piece c is the B fragment pair of MMAs (c, 0) = words x, y and
-// (c, 1) = words z, w; the query piece at the same offset gives the matching A fragments.
-// V of the group: lane (g, j) loads, for tokens 2j, 2j+1, 2j+8, 2j+9, the pieces
-// [q*64 + g*8, +8), q < D/64: eight lanes cover 128 contiguous bytes of a row.  Element e of the
-// piece, taken from the four tokens, is the B fragment of MMA (q, e), whose output column of
-// lane j is head element q*64 + 16j + e (c0) and q*64 + 16j + 8 + e (c1).
-template <typename T, int D>
-__global__ void __launch_bounds__(kMmaWarps * 32, kMmaCtasPerSm)
-kv_attention_mma_kernel(int* __restrict__ plan, const int* __restrict__ part_offset,
+// ---- K/V streaming fed by tensor copies -------------------------------------------------
+// A register-staged version of this kernel (16-byte ld.global per lane, the loaded vectors used
+// as MMA fragments directly) kept 98 KB of loads in flight per SM and every byte passed the
+// load/store unit: inside a decode step, at the ~1 GHz SM clock the power cap leaves, that was
+// worth ~29 bytes per SM clock (4.3 TB/s), while the tensor-copy (TMA) path of the re-projection
+// kernel delivers 60.  Here the 16-token groups arrive by cp.async.bulk.tensor: the K (V) plane is a
+// 3-D tensor [head-row halves of 64 elements][cache rows][64 elements], one box of
+// (64, 16 rows, D/64 halves) = one cache block's 16 rows of one head lands in shared memory as
+// [half][token][128 bytes] with the 128-byte swizzle, so that ldmatrix reads it without bank
+// conflicts: plain ldmatrix gives the B fragments of Q K^T, ldmatrix.trans those of P V (no
+// byte permutes).  One elected lane per warp issues two copies per group (K box, V box) on the
+// warp's own ring of stages, each with its mbarrier; the stream of groups continues across
+// work units.  Rows of the last cache block past the sequence length arrive too: their scores
+// are masked and their V rows are zeroed in shared memory before use.
+#ifndef APS_KV_WARPS
+#define APS_KV_WARPS 8
+#endif
+#ifndef APS_KV_STAGES
+#define APS_KV_STAGES 3
+#endif
+// 8 warps with a ring of 3 groups each (193 KB of shared memory at head size 128, one CTA per SM)
+// measured best on OPT-13B rows: 6.57 TB/s alone, 5.7 - 5.8 TB/s inside the loaded step; 4 warps x 3
+// x 2 CTAs: 5.9 / 5.2; 12 warps x 2: 4.9 / 4.3; 6 warps x 4: 6.1 / 4.4; 5 warps x 5: 6.0 / 4.0.
+constexpr int kTmaWarps = APS_KV_WARPS;
+constexpr int kStatusKvWait = 5;   // a bounded wait for a K/V tensor copy ran out
+constexpr long long kKvWaitBudget = 2000000000LL;
+
+template <int DS>
+struct TmaUnit {
+  int n_groups;              // 16-token groups (0 = no unit)
+  int tok_begin, tok_end;
+  int my_row;                // lane l: first cache row (block * block_size + offset) of the unit's group l
+  int head_coord;            // h * (D / 64): coordinate of the head in the third tensor dimension
+  int64_t slot;              // where the unit's partial goes
+  uint32_t qa[DS][2];        // A fragments (a0, a2) of the query row per 16-element step (lanes 0..3)
+};
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+template <typename T, int D, int S>
+__global__ void __launch_bounds__(kTmaWarps * 32, (384 / (kTmaWarps * 32)) > 0 ? (384 / (kTmaWarps * 32)) : 1)
+kv_attention_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                        int* __restrict__ plan, const int* __restrict__ part_offset,
                         const int2* __restrict__ kv_chunks, float* __restrict__ part_ml,
                         float* __restrict__ part_acc, const T* __restrict__ query,
-                        const T* __restrict__ key_cache, const T* __restrict__ value_cache,
                         const int32_t* __restrict__ block_tables, const int32_t* __restrict__ seq_lens,
                         int max_blocks_per_seq, int heads, int block_size, int64_t query_stride,
-                        int64_t block_stride, float scale_log2) {
-  static_assert(sizeof(T) == 2 && (D == 64 || D == 128), "tensor-core streaming kernel: 2-byte types, head size 64 or 128");
-  constexpr int NC = D / 32;   // 16-byte K pieces per lane and token
-  constexpr int NQ = D / 64;   // 16-byte V pieces per lane and token
+                        float scale_log2) {
+  static_assert(sizeof(T) == 2 && (D == 64 || D == 128), "2-byte types, head size 64 or 128");
+  constexpr int DS = D / 16;                  // 16-element steps of the head dimension
+  constexpr int kHalves = D / 64;
+  constexpr int kTileBytes = 16 * D * 2;      // K (or V) of one group: [half][token][128 B]
+  constexpr int kStageBytes = 2 * kTileBytes;
   using M = Mma16816<T>;
-  const int lane = threadIdx.x & 31;
+  using Unit = TmaUnit<DS>;
+  extern __shared__ unsigned char ring_raw[];
+  __shared__ uint64_t bars[kTmaWarps][S];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, j = lane & 3;
   const int total = plan[kPlanNumKvChunks] * heads;
-  const int64_t row_stride = (int64_t)heads * D;
+  const uint32_t ring = (((uint32_t)__cvta_generic_to_shared(ring_raw) + 1023u) & ~1023u) + warp * (S * kStageBytes);
+  const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(&bars[warp][0]);
+  if (lane == 0) {
+    for (int st = 0; st < S; ++st)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar0 + st * 8) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncwarp();
 
-  int unit = 0;
-  if (lane == 0) unit = atomicAdd(&plan[kPlanKvCounter], 1);
-  unit = __shfl_sync(kFull, unit, 0);
-  while (unit < total) {
-    // the next unit's index is fetched while this one is streamed
-    int next_unit = 0;
-    if (lane == 0) next_unit = atomicAdd(&plan[kPlanKvCounter], 1);
-
-    const int2 rc = kv_chunks[unit / heads];
-    const int h = unit % heads;
-    const int req = rc.x;
-    const int seq = min(seq_lens[req], max_blocks_per_seq * block_size);
-    const int tok_begin = rc.y * kChunkTokens;
-    const int tok_end = min(seq, tok_begin + kChunkTokens);
-    const int n_groups = (tok_end - tok_begin + kGroupTokens - 1) / kGroupTokens;
-    // block-table entry of each of the chunk's groups (a group never straddles a cache block:
-    // block sizes are multiples of 16), one per lane, handed out by shuffle
-    int my_blk = 0;
-    if (lane < n_groups)
-      my_blk = block_tables[(int64_t)req * max_blocks_per_seq + (tok_begin + lane * kGroupTokens) / block_size];
-
-    // A fragments of the query row (lanes 0..3 = row 0; the other rows are zero)
-    uint32_t qa[NC][4];
+  auto next_index = [&]() {
+    int idx = 0;
+    if (lane == 0) idx = atomicAdd(&plan[kPlanKvCounter], 1);
+    return __shfl_sync(kFull, idx, 0);
+  };
+  auto load_unit = [&](int idx) {
+    Unit u;
+    u.n_groups = 0; u.tok_begin = u.tok_end = 0; u.my_row = 0; u.head_coord = 0; u.slot = 0;
 #pragma unroll
-    for (int c = 0; c < NC; ++c) {
-      uint4 qv = make_uint4(0, 0, 0, 0);
-      if (g == 0) qv = *reinterpret_cast<const uint4*>(query + req * query_stride + h * D + c * 32 + j * 8);
-      qa[c][0] = qv.x; qa[c][1] = qv.y; qa[c][2] = qv.z; qa[c][3] = qv.w;
+    for (int st = 0; st < DS; ++st) u.qa[st][0] = u.qa[st][1] = 0u;
+    if (idx < total) {
+      const int2 rc = kv_chunks[idx / heads];
+      const int h = idx % heads, req = rc.x;
+      const int seq = min(seq_lens[req], max_blocks_per_seq * block_size);
+      u.tok_begin = rc.y * kChunkTokens;
+      u.tok_end = min(seq, u.tok_begin + kChunkTokens);
+      u.n_groups = (u.tok_end - u.tok_begin + kGroupTokens - 1) / kGroupTokens;
+      if (lane < u.n_groups) {
+        const int tb = u.tok_begin + lane * kGroupTokens;   // a group never straddles a cache block
+        u.my_row = block_tables[(int64_t)req * max_blocks_per_seq + tb / block_size] * block_size + tb % block_size;
+      }
+      u.head_coord = h * kHalves;
+      u.slot = (int64_t)(part_offset[req] + rc.y) * heads + h;
+      if (g == 0) {
+        const T* q = query + req * query_stride + h * D + 2 * j;
+#pragma unroll
+        for (int st = 0; st < DS; ++st) {
+          u.qa[st][0] = *reinterpret_cast<const uint32_t*>(q + 16 * st);
+          u.qa[st][1] = *reinterpret_cast<const uint32_t*>(q + 16 * st + 8);
+        }
+      }
     }
-    float acc[NQ][8][2];
+    return u;
+  };
+  // request group gi of unit u into ring stage `stage`: two boxes counted on the stage's barrier
+  auto issue_group = [&](const Unit& u, int gi, uint32_t stage) {
+    const int row = __shfl_sync(kFull, u.my_row, gi);
+    if (lane == 0) {
+      const uint32_t bar = bar0 + stage * 8, dst = ring + stage * kStageBytes;
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(kStageBytes) : "memory");
+      asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                   ::"r"(dst), "l"(reinterpret_cast<uint64_t>(&map_k)), "r"(bar), "r"(0), "r"(row), "r"(u.head_coord) : "memory");
+      asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                   ::"r"(dst + kTileBytes), "l"(reinterpret_cast<uint64_t>(&map_v)), "r"(bar), "r"(0), "r"(row), "r"(u.head_coord) : "memory");
+    }
+  };
+  auto try_wait = [&](uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+  };
+  // the whole warp tests once; if the data is not there lane 0 waits (bounded) and tells the others
+  auto wait_stage = [&](uint32_t stage, uint32_t parity) {
+    const uint32_t bar = bar0 + stage * 8;
+    if (__all_sync(kFull, try_wait(bar, parity))) return true;
+    bool got = true;
+    if (lane == 0) {
+      const long long t0 = clock64();
+      int spins = 0;
+      while (!try_wait(bar, parity)) {
+        if ((++spins & 255) == 0 && clock64() - t0 > kKvWaitBudget) { got = false; break; }
+      }
+    }
+    got = __shfl_sync(kFull, got ? 1 : 0, 0) != 0;
+    if (got) (void)try_wait(bar, parity);   // every lane observes the completed phase itself
+    return got;
+  };
+
+  Unit cur = load_unit(next_index());
+  Unit nxt = load_unit(next_index());
+  int issue_in_nxt = 0, issue_g = 0;       // the request cursor: unit (cur / nxt) and group
+  uint32_t issued = 0, consumed = 0;       // groups requested / used so far (ring stage = count % S)
+  auto refill = [&]() {
+    while (issued - consumed < (uint32_t)S) {
+      if (!issue_in_nxt && issue_g >= cur.n_groups) { issue_in_nxt = 1; issue_g = 0; }
+      if (issue_in_nxt && issue_g >= nxt.n_groups) break;   // nothing known beyond the next unit yet
+      if (issue_in_nxt) issue_group(nxt, issue_g, issued % S);
+      else issue_group(cur, issue_g, issued % S);
+      ++issue_g; ++issued;
+    }
+  };
+  refill();
+
+  // per-lane parts of the ldmatrix addresses (row inside an 8-row group, 16-byte piece)
+  const int lrow = lane & 7, lmat = lane >> 3;
+  bool ok = true;
+  while (cur.n_groups > 0 && ok) {
+    float acc[D / 8][2];
 #pragma unroll
-    for (int q = 0; q < NQ; ++q)
-#pragma unroll
-      for (int e = 0; e < 8; ++e) acc[q][e][0] = acc[q][e][1] = 0.f;
+    for (int nb = 0; nb < D / 8; ++nb) acc[nb][0] = acc[nb][1] = 0.f;
     float m = -INFINITY, l = 0.f;
 
-    const T* k_head = key_cache + h * D + j * 8;     // + block and row offsets
-    const T* v_head = value_cache + h * D + g * 8;
-    uint4 kreg[2][NC], vreg[4][NQ];
-    auto load_k = [&](int gi) {
-      const int blk = __shfl_sync(kFull, my_blk, gi);
-      const int tb = tok_begin + gi * kGroupTokens;
-      const T* base = k_head + (int64_t)blk * block_stride + (int64_t)(tb % block_size + g) * row_stride;
-#pragma unroll
-      for (int b = 0; b < 2; ++b) {
-        const bool live = tb + b * 8 + g < tok_end;
-#pragma unroll
-        for (int c = 0; c < NC; ++c)
-          kreg[b][c] = live ? ld_stream16(base + (int64_t)b * 8 * row_stride + c * 32) : make_uint4(0, 0, 0, 0);
+    for (int gi = 0; gi < cur.n_groups; ++gi) {
+      const uint32_t stage = consumed % S;
+      if (!wait_stage(stage, (consumed / S) & 1u)) { ok = false; break; }
+      const uint32_t ktile = ring + stage * kStageBytes, vtile = ktile + kTileBytes;
+      const int tb = cur.tok_begin + gi * kGroupTokens;
+      const int n_valid = min(kGroupTokens, cur.tok_end - tb);
+      if (n_valid < kGroupTokens) {
+        // rows past the sequence length hold whatever the cache block holds: zero them in V
+        // (their scores are masked below, and 0 * garbage must stay 0)
+        const int n_pieces = (kGroupTokens - n_valid) * kHalves * 8;
+        for (int i = lane; i < n_pieces; i += 32) {
+          const int r = n_valid + i / (kHalves * 8), rem = i % (kHalves * 8);
+          const uint32_t a = vtile + (rem >> 3) * 2048 + r * 128 + (rem & 7) * 16;
+          asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(a), "r"(0u) : "memory");
+        }
+        __syncwarp();
       }
-    };
-    auto load_v = [&](int gi) {
-      const int blk = __shfl_sync(kFull, my_blk, gi);
-      const int tb = tok_begin + gi * kGroupTokens;
-      const T* base = v_head + (int64_t)blk * block_stride + (int64_t)(tb % block_size + 2 * j) * row_stride;
-#pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        const int off = (t & 1) + (t >> 1) * 8;            // tokens 2j, 2j+1, 2j+8, 2j+9 of the group
-        const bool live = tb + 2 * j + off < tok_end;
-#pragma unroll
-        for (int q = 0; q < NQ; ++q)
-          vreg[t][q] = live ? ld_stream16(base + (int64_t)off * row_stride + q * 64) : make_uint4(0, 0, 0, 0);
-      }
-    };
-
-    load_k(0);
-    for (int gi = 0; gi < n_groups; ++gi) {
-      load_v(gi);
       // ---- scores of the group's two 8-token blocks: row 0 of Q K^T ----
       float sc[2][2][2];   // [block][partial chain][column]
 #pragma unroll
       for (int b = 0; b < 2; ++b) {
         sc[b][0][0] = sc[b][0][1] = sc[b][1][0] = sc[b][1][1] = 0.f;
+        const int r = b * 8 + lrow;
 #pragma unroll
-        for (int c = 0; c < NC; ++c) {
-          M::run(sc[b][0][0], sc[b][0][1], qa[c][0], qa[c][1], kreg[b][c].x, kreg[b][c].y);
-          M::run(sc[b][1][0], sc[b][1][1], qa[c][2], qa[c][3], kreg[b][c].z, kreg[b][c].w);
+        for (int c4 = 0; c4 < D / 32; ++c4) {
+          const int piece = 4 * c4 + lmat;
+          uint32_t kf[4];
+          ldmatrix_x4(ktile + (piece >> 3) * 2048 + r * 128 + (((piece & 7) ^ (r & 7)) << 4), kf);
+          M::run(sc[b][0][0], sc[b][0][1], cur.qa[2 * c4][0], cur.qa[2 * c4][1], kf[0], kf[1]);
+          M::run(sc[b][1][0], sc[b][1][1], cur.qa[2 * c4 + 1][0], cur.qa[2 * c4 + 1][1], kf[2], kf[3]);
         }
       }
-      if (gi + 1 < n_groups) load_k(gi + 1);
       // ---- online softmax over the 16 tokens (lane j of row 0: tokens 2j, 2j+1 of each block) ----
-      const int tb = tok_begin + gi * kGroupTokens;
       float s[2][2];
       float gm = -INFINITY;
 #pragma unroll
@@ -464,7 +553,7 @@ kv_attention_mma_kernel(int* __restrict__ plan, const int* __restrict__ part_off
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
           const float v = (sc[b][0][i] + sc[b][1][i]) * scale_log2;
-          s[b][i] = tb + b * 8 + 2 * j + i < tok_end ? v : -INFINITY;
+          s[b][i] = b * 8 + 2 * j + i < n_valid ? v : -INFINITY;
           gm = fmaxf(gm, s[b][i]);
         }
       gm = fmaxf(gm, __shfl_xor_sync(kFull, gm, 1));
@@ -480,35 +569,49 @@ kv_attention_mma_kernel(int* __restrict__ plan, const int* __restrict__ part_off
       l = l * corr + (p[0][0] + p[0][1]) + (p[1][0] + p[1][1]);
       // the score fragment, rounded to the cache's type, is the A fragment of P V
       const uint32_t pa0 = M::pack(p[0][0], p[0][1]), pa2 = M::pack(p[1][0], p[1][1]);
-      // ---- weighted V rows: row 0 of P V ----
+      // ---- weighted V rows: row 0 of P V; one transposed ldmatrix per 16 head elements ----
+      {
+        const int r = (lmat & 1) * 8 + lrow;
 #pragma unroll
-      for (int q = 0; q < NQ; ++q)
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const uint32_t sel = (e & 1) ? 0x7632u : 0x5410u;
-          const uint32_t b0 = __byte_perm(word_of(vreg[0][q], e >> 1), word_of(vreg[1][q], e >> 1), sel);
-          const uint32_t b1 = __byte_perm(word_of(vreg[2][q], e >> 1), word_of(vreg[3][q], e >> 1), sel);
-          acc[q][e][0] *= corr; acc[q][e][1] *= corr;
-          M::run(acc[q][e][0], acc[q][e][1], pa0, pa2, b0, b1);
+        for (int n2 = 0; n2 < D / 16; ++n2) {
+          const int piece = 2 * n2 + (lmat >> 1);
+          uint32_t vf[4];
+          ldmatrix_x4_trans(vtile + (piece >> 3) * 2048 + r * 128 + (((piece & 7) ^ (r & 7)) << 4), vf);
+          acc[2 * n2][0] *= corr; acc[2 * n2][1] *= corr;
+          acc[2 * n2 + 1][0] *= corr; acc[2 * n2 + 1][1] *= corr;
+          M::run(acc[2 * n2][0], acc[2 * n2][1], pa0, pa2, vf[0], vf[1]);
+          M::run(acc[2 * n2 + 1][0], acc[2 * n2 + 1][1], pa0, pa2, vf[2], vf[3]);
         }
+      }
+      // every lane's reads of the stage are done (their results fed MMAs): it can be refilled.
+      // After the zero fill above the next tensor copy follows generic stores to the stage.
+      __syncwarp();
+      if (n_valid < kGroupTokens && lane == 0) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      ++consumed;
+      refill();
     }
-    // ---- the partial: lanes 0..3 hold row 0 ----
+    if (!ok) break;
+    // ---- the partial: lanes 0..3 hold row 0 (lane j: head elements nb*8 + 2j, 2j + 1) ----
     l += __shfl_xor_sync(kFull, l, 1);
     l += __shfl_xor_sync(kFull, l, 2);
     if (g == 0) {
-      const int64_t slot = (int64_t)(part_offset[req] + rc.y) * heads + h;
+      float* dst = part_acc + cur.slot * D + 2 * j;
 #pragma unroll
-      for (int q = 0; q < NQ; ++q) {
-        float* dst = part_acc + slot * D + q * 64 + 16 * j;
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          *reinterpret_cast<float4*>(dst + 8 * i) = make_float4(acc[q][0][i], acc[q][1][i], acc[q][2][i], acc[q][3][i]);
-          *reinterpret_cast<float4*>(dst + 8 * i + 4) = make_float4(acc[q][4][i], acc[q][5][i], acc[q][6][i], acc[q][7][i]);
-        }
-      }
-      if (lane == 0) *reinterpret_cast<float2*>(part_ml + slot * 2) = make_float2(m, l);
+      for (int nb = 0; nb < D / 8; ++nb) *reinterpret_cast<float2*>(dst + nb * 8) = make_float2(acc[nb][0], acc[nb][1]);
+      if (lane == 0) *reinterpret_cast<float2*>(part_ml + cur.slot * 2) = make_float2(m, l);
     }
-    unit = __shfl_sync(kFull, next_unit, 0);
+    // the next unit becomes the current one; the request cursor keeps its place in it
+    cur = nxt;
+    if (issue_in_nxt) issue_in_nxt = 0; else issue_g = 0;
+    nxt = load_unit(cur.n_groups > 0 ? next_index() : total);
+    refill();
+  }
+  if (!ok) {
+    // a copy never arrived: record it (the combine kernel then marks the output) and give the
+    // copies still in flight a bounded time to land before the CTA's shared memory is released
+    if (lane == 0) atomicCAS(&plan[kPlanStatus], 0, kStatusKvWait);
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) { }
   }
 }
 
@@ -563,20 +666,59 @@ combine_kernel(const int* __restrict__ plan, const int* __restrict__ part_offset
   }
 }
 
+// Tensor maps of the K and V planes for the tensor-copy kernel: [64 elements][cache rows][row
+// halves of 64 elements], box (64, 16 rows, D / 64).  The number of cache rows is not part of the
+// C ABI (block ids come from the block tables), so the row dimension is given a bound far above
+// any cache; the copies only ever name rows of blocks that the block tables hold.
+template <int D>
+int kv_plane_maps(const void* key_cache, const void* value_cache, const AttnShape& s, CUtensorMap* mk, CUtensorMap* mv) {
+  TensorMapSpec spec{};
+  spec.dtype = s.dtype; spec.rank = 3;
+  spec.dims[0] = 64; spec.dims[1] = uint64_t(1) << 26; spec.dims[2] = (uint64_t)s.heads * D / 64;
+  spec.strides_bytes[0] = (uint64_t)s.heads * D * 2; spec.strides_bytes[1] = 128;
+  spec.box[0] = 64; spec.box[1] = 16; spec.box[2] = D / 64;
+  spec.base = key_cache;
+  int st = cached_tensor_map(mk, spec, "K plane");
+  if (st != APS_OK) return st;
+  spec.base = value_cache;
+  return cached_tensor_map(mv, spec, "V plane");
+}
+
 template <typename T, int D>
 int launch_kv_typed(const WorkspacePtrs& ws, const void* query, const void* key_cache,
                     const void* value_cache, const int32_t* block_tables, const int32_t* seq_lens,
                     const AttnShape& s, cudaStream_t stream) {
   const float scale_log2 = s.scale * 1.4426950408889634f;
-  ScopedProfile prof(0, stream);
   if constexpr (sizeof(T) == 2 && (D == 64 || D == 128)) {
-    // tensor-core arithmetic: 3 persistent CTAs of 4 warps per SM
-    kv_attention_mma_kernel<T, D><<<sm_count() * kMmaCtasPerSm, kMmaWarps * 32, 0, stream>>>(
-        ws.plan, ws.part_offset, ws.kv_chunks, ws.part_ml, ws.part_acc, (const T*)query,
-        (const T*)key_cache, (const T*)value_cache, block_tables, seq_lens, s.max_blocks_per_seq,
-        s.heads, s.block_size, s.query_stride, s.block_stride, scale_log2);
-    return launch_status("kv_attention_mma_kernel");
+    // blocks laid out back to back ([NB, BS, H, D] contiguous, what the cache engine allocates):
+    // cache row = block * BS + offset, and the tensor-copy kernel applies
+    if (s.block_stride == (int64_t)s.block_size * s.heads * D) {
+      constexpr int kStages = APS_KV_STAGES;
+      constexpr int kSmem = 1024 + kTmaWarps * kStages * (2 * 16 * D * 2);
+      auto kernel = kv_attention_tma_kernel<T, D, kStages>;
+      static bool attr_set[64] = {false};
+      int dev = 0;
+      APS_CUDA(cudaGetDevice(&dev));
+      APS_REQUIRE(dev >= 0 && dev < 64, APS_ERR_CUDA, "device index %d out of range", dev);
+      if (!attr_set[dev]) {
+        APS_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+        APS_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+        attr_set[dev] = true;
+      }
+      CUtensorMap mk, mv;
+      int st = kv_plane_maps<D>(key_cache, value_cache, s, &mk, &mv);
+      if (st != APS_OK) return st;
+      ScopedProfile prof(0, stream);
+      int per_sm = 0;
+      APS_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kTmaWarps * 32, kSmem));
+      APS_REQUIRE(per_sm > 0, APS_ERR_CUDA, "the K/V streaming kernel does not fit on this device");
+      kernel<<<sm_count() * per_sm, kTmaWarps * 32, kSmem, stream>>>(
+          mk, mv, ws.plan, ws.part_offset, ws.kv_chunks, ws.part_ml, ws.part_acc, (const T*)query, block_tables,
+          seq_lens, s.max_blocks_per_seq, s.heads, s.block_size, s.query_stride, scale_log2);
+      return launch_status("kv_attention_tma_kernel");
+    }
   }
+  ScopedProfile prof(0, stream);
   // CUDA-core arithmetic: 2 persistent CTAs of 8 warps per SM
   const int grid = sm_count() * 2;
   const int threads = kKvWarps * 32;

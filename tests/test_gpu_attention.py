@@ -71,6 +71,24 @@ def test_paged_decode_attention_block_size_32_and_garbage_tail():
     assert_close(out, ref, "block size 32")
 
 
+def test_paged_decode_attention_padded_block_stride():
+    """Cache blocks that are not laid out back to back (a view with 128 bytes of padding after
+    every block): the tensor-copy kernel does not apply and the CUDA-core kernel takes over."""
+    shape = LayerShape("t", 3, 128, 384, torch.float16)
+    lens = [1, 17, 130, 700]
+    w = make_decode_workload(shape, lens, [False] * len(lens), seed=12)
+    ref = O.paged_decode_attention(w.query, w.kv_cache[0], w.kv_cache[1], w.meta.block_tables,
+                                   w.meta.seq_lens_tensor, w.scale)
+    dev = w.to("cuda")
+    nb, bs, h, d = dev.kv_cache.shape[1:]
+    padded = torch.zeros(2, nb, bs * h * d + 64, dtype=torch.float16, device="cuda")
+    padded[:, :, :bs * h * d] = dev.kv_cache.view(2, nb, -1)
+    kc, vc = (padded[p, :, :bs * h * d].view(nb, bs, h, d) for p in (0, 1))
+    assert kc.stride(0) == bs * h * d + 64
+    out = A.paged_decode_attention(dev.query, kc, vc, dev.meta.block_tables, dev.meta.seq_lens_tensor, dev.scale)
+    assert_close(out, ref, "padded block stride")
+
+
 def test_unsupported_head_size_raises():
     q = torch.zeros(1, 2 * 96, dtype=torch.float16, device="cuda")
     kc = torch.zeros(2, 16, 2, 96, dtype=torch.float16, device="cuda")
