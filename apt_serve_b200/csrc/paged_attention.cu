@@ -668,13 +668,13 @@ combine_kernel(const int* __restrict__ plan, const int* __restrict__ part_offset
 
 // Tensor maps of the K and V planes for the tensor-copy kernel: [64 elements][cache rows][row
 // halves of 64 elements], box (64, 16 rows, D / 64).  The number of cache rows is not part of the
-// C ABI (block ids come from the block tables), so the row dimension is given a bound far above
-// any cache; the copies only ever name rows of blocks that the block tables hold.
+// C ABI (block ids come from the block tables), so the row dimension is given the largest bound a
+// 32-bit row coordinate can reach; the copies only ever name rows of blocks that the block tables hold.
 template <int D>
 int kv_plane_maps(const void* key_cache, const void* value_cache, const AttnShape& s, CUtensorMap* mk, CUtensorMap* mv) {
   TensorMapSpec spec{};
   spec.dtype = s.dtype; spec.rank = 3;
-  spec.dims[0] = 64; spec.dims[1] = uint64_t(1) << 26; spec.dims[2] = (uint64_t)s.heads * D / 64;
+  spec.dims[0] = 64; spec.dims[1] = uint64_t(1) << 31; spec.dims[2] = (uint64_t)s.heads * D / 64;
   spec.strides_bytes[0] = (uint64_t)s.heads * D * 2; spec.strides_bytes[1] = 128;
   spec.box[0] = 64; spec.box[1] = 16; spec.box[2] = D / 64;
   spec.base = key_cache;
