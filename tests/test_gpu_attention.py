@@ -55,20 +55,21 @@ def test_paged_decode_attention(dtype, heads, head_dim):
     assert_close(out, ref, f"paged decode {dtype} H{heads} D{head_dim}", tol, tol)
 
 
-def test_paged_decode_attention_block_size_32_and_garbage_tail():
-    # block size 32; slots past seq_len inside the last block hold NaN and must not leak
-    shape = LayerShape("t", 2, 128, 256, torch.float16, block_size=32)
-    lens = [5, 33, 70]
-    w = make_decode_workload(shape, lens, [False] * 3, seed=8)
+@pytest.mark.parametrize("bs", [32, 64, 256])
+def test_paged_decode_attention_larger_blocks_and_garbage_tail(bs):
+    # larger cache blocks; slots past seq_len inside the last block hold NaN and must not leak
+    shape = LayerShape("t", 2, 128, 256, torch.float16, block_size=bs)
+    lens = [5, 33, 70, 300, 257]
+    w = make_decode_workload(shape, lens, [False] * len(lens), seed=8)
     for r, s in enumerate(lens):
         blk = w.block_tables[r][-1]
-        w.kv_cache[:, blk, s % 32 or 32:] = float("nan")
+        w.kv_cache[:, blk, s % bs or bs:] = float("nan")
     ref = O.paged_decode_attention(w.query, w.kv_cache[0], w.kv_cache[1], w.meta.block_tables,
                                    w.meta.seq_lens_tensor, w.scale)
     dev = w.to("cuda")
     out = A.paged_decode_attention(dev.query, dev.kv_cache[0], dev.kv_cache[1],
                                    dev.meta.block_tables, dev.meta.seq_lens_tensor, dev.scale)
-    assert_close(out, ref, "block size 32")
+    assert_close(out, ref, f"block size {bs}")
 
 
 def test_paged_decode_attention_padded_block_stride():
@@ -142,6 +143,18 @@ def test_hybrid_small(dtype):
     ref = oracle_out(w)
     out = gpu_hybrid(w.to("cuda"))
     assert_close(out, ref, f"hybrid small {dtype}")
+
+
+@pytest.mark.parametrize("bs", [32, 64])
+def test_hybrid_larger_cache_blocks(bs):
+    """Cache blocks of 32 / 64 tokens: a hidden request's 16-row sub-blocks then sit at offsets
+    inside a block, K/V groups likewise."""
+    shape = LayerShape("t", 2, 128, 256, torch.float16, block_size=bs)
+    lens, hid = [5, 40, 17, 129, 300, 64, 65], [True, False, True, False, True, True, False]
+    w = make_decode_workload(shape, lens, hid, seed=4)
+    ref = oracle_out(w)
+    out = gpu_hybrid(w.to("cuda"))
+    assert_close(out, ref, f"hybrid, block size {bs}")
 
 
 @pytest.mark.parametrize("hidden_fraction", [0.0, 1.0])
