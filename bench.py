@@ -393,17 +393,6 @@ def kernel_rooflines(work, res, peaks):
     return hidden, kv
 
 
-def slim(res, keys=("ms_per_step", "kv_ms", "hid_ms", "pf_ms")):
-    out = {}
-    for k in keys:
-        if res.get(k) is not None:
-            out[k] = round(res[k], 4)
-    for k in ("clocks", "ms_x_sm_mhz"):
-        if k in res:
-            out[k] = res[k]
-    return out
-
-
 # --------------------------------------------------------------------------- #
 # end to end through the public API with host buffers
 # --------------------------------------------------------------------------- #
