@@ -67,8 +67,10 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """One nvidia-smi process sampling SM clock, power and throttle reasons every 100 ms for
-    the life of the benchmark; ``window(t0, t1)`` summarises the samples of a time window."""
+    """Samples SM clock, board power and the clock-event (throttle) reasons of one GPU for the life
+    of the benchmark -- through NVML every 10 ms where the bindings import (read-only queries, the
+    same counters nvidia-smi prints), else through one ``nvidia-smi -lms 100`` process;
+    ``window(t0, t1)`` summarises the samples of a time window."""
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -77,64 +79,108 @@ class ClockSampler:
     def __init__(self, gpu_index: int):
         self.gpu_index = gpu_index
         self.proc = None
-        self.lines = []          # (arrival time, text)
-        self.reader = None
+        self.samples = []        # (arrival time, sm MHz, max sm MHz, watts, set of reasons)
+        self.thread = None
+        self.stopping = False
+        self.source = None
 
-    def start(self):
+    # -- NVML ------------------------------------------------------------------------ #
+    def _start_nvml(self):
+        import pynvml
+        pynvml.nvmlInit()
+        handle = None
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100", "-i", str(self.gpu_index)],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True, bufsize=1)
-        except OSError:
-            self.proc = None
-            return
+            uuid = str(torch.cuda.get_device_properties(self.gpu_index).uuid)
+            handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if not uuid.startswith("GPU-") else uuid)
+        except Exception:
+            handle = pynvml.nvmlDeviceGetHandleByIndex(self.gpu_index)
+        reasons_fn = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons",
+                             getattr(pynvml, "nvmlDeviceGetCurrentClocksThrottleReasons", None))
+        bits = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
+        mx = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+        pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)   # fails here, not in the thread
+
+        def pump():
+            while not self.stopping:
+                try:
+                    mhz = float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM))
+                    watts = pynvml.nvmlDeviceGetPowerUsage(handle) / 1000.0
+                    mask = int(reasons_fn(handle)) if reasons_fn is not None else 0
+                    self.samples.append((time.perf_counter(), mhz, mx, watts,
+                                         {n for n, b in bits.items() if mask & b}))
+                except Exception:
+                    pass
+                time.sleep(0.01)
+
+        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread.start()
+        self.source = "NVML, every 10 ms"
+
+    # -- nvidia-smi -------------------------------------------------------------------- #
+    def _start_smi(self):
+        self.proc = subprocess.Popen(
+            ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+             "-lms", "100", "-i", str(self.gpu_index)],
+            stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True, bufsize=1)
 
         def pump():
             for line in self.proc.stdout:
-                self.lines.append((time.perf_counter(), line))
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    self.samples.append((time.perf_counter(), float(f[1]), float(f[2]), float(f[3]),
+                                         {n for n, v in zip(self.NAMES, f[5:9]) if v.lower().startswith("active")}))
+                except ValueError:
+                    continue
 
-        self.reader = threading.Thread(target=pump, daemon=True)
-        self.reader.start()
+        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread.start()
+        self.source = "nvidia-smi -lms 100"
+
+    def start(self):
+        try:
+            self._start_nvml()
+        except Exception:
+            try:
+                self._start_smi()
+            except OSError:
+                self.source = None
+
+    @property
+    def lines(self):
+        return self.samples
 
     def stop(self):
-        if self.proc is None:
-            return
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        self.reader.join(timeout=2)
+        self.stopping = True
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        if self.thread is not None:
+            self.thread.join(timeout=2)
 
     def window(self, t_begin: float, t_end: float, lead: float = 0.0):
         """Samples that arrived in ``[t_begin, t_end]``.  A window shorter than the sampling
         interval may hold none: then the samples of the ``lead`` seconds of identical load
         just before it are used and ``window`` says so."""
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        inside = [ln for t, ln in self.lines if t_begin <= t <= t_end + 0.02]
+        if self.source is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no clock source available"]}
+        inside = [x for x in self.samples if t_begin <= x[0] <= t_end + 0.005]
         where = "timed region"
         if not inside and lead > 0:
-            inside = [ln for t, ln in self.lines if t_begin - lead <= t < t_begin]
+            inside = [x for x in self.samples if t_begin - lead <= x[0] < t_begin]
             where = f"untimed steps of the same load in the {lead:.1f} s before the timed region (region shorter than the sampling interval)"
-        sm, mx, reasons, power = [], [], set(), []
-        for line in inside:
-            f = [x.strip() for x in line.split(",")]
-            if len(f) < 9:
-                continue
-            try:
-                sm.append(float(f[1])); mx.append(float(f[2])); power.append(float(f[3]))
-            except ValueError:
-                continue
-            for name, v in zip(self.NAMES, f[5:9]):
-                if v.lower().startswith("active"):
-                    reasons.add(name)
-        if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
-                "samples": len(sm), "power_w_max": max(power) if power else None,
-                "power_w_median": statistics.median(power) if power else None, "window": where}
+        if not inside:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"], "source": self.source}
+        sm = [x[1] for x in inside]
+        power = [x[3] for x in inside]
+        reasons = set().union(*[x[4] for x in inside])
+        return {"sm_mhz": statistics.median(sm), "sm_min_mhz": min(sm), "sm_max_mhz": max(x[2] for x in inside),
+                "reasons": sorted(reasons), "samples": len(sm), "power_w_max": round(max(power), 1),
+                "power_w_median": round(statistics.median(power), 1), "window": where, "source": self.source}
 
 
 def dist_env():
