@@ -512,6 +512,7 @@ class EndToEnd:
         self.slots[(steps - 1) & 1]["d2h"].synchronize()
         barrier()
         sec = (time.perf_counter() - t0) / steps
+        self.last_result = self.slots[(steps - 1) & 1]["out"]
         t = torch.tensor([sec], device=self.dev, dtype=torch.float64)
         if self.tp > 1:
             torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
@@ -600,6 +601,8 @@ def run_ours(args):
     e2e = EndToEnd(st, dev, tp, out_shape, shape.dtype)
     e2e_s = e2e.run(K, timer.barrier)
     h2d_bytes, d2h_bytes = e2e.h2d_bytes, e2e.d2h_bytes
+    # what arrived on the host is what the device-resident step computes from the same inputs
+    e2e_diff = float((e2e.last_result.float() - st.step().float().cpu()).abs().max())
     status |= st.A.attention_status(st.workspace)
 
     line_extra = {}
@@ -769,6 +772,7 @@ def run_ours(args):
         "clocks": res.get("clocks"), "ms_x_sm_mhz": res.get("ms_x_sm_mhz"),
         "e2e": {"value": round(B / e2e_s, 2), "unit": UNIT, "h2d_bytes_per_step": h2d_bytes,
                 "d2h_bytes_per_step": d2h_bytes, "ms_per_step": round(e2e_s * 1e3, 4),
+                "max_abs_diff_vs_device_resident_step": e2e_diff,
                 "pipeline": "two steps in flight: one pinned staging buffer and one host-to-device copy per step on "
                             "a side stream, the step and the device-to-host copy of its result on the main stream; "
                             "the host waits for step i - 1's result before it enqueues step i + 1"},
