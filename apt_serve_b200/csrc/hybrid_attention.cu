@@ -59,7 +59,8 @@ namespace {
 
 constexpr int kBM = 128;          // token rows per tile (per CTA)
 constexpr int kBN = 256;          // K_h | V_h columns
-constexpr int kHeadDim = 128;
+constexpr int kHeadDim = 128;      // columns of K (and of V) in one tile: one head of 128, two of 64, four of 32
+constexpr int kMaxHeadsPerTile = 4;
 constexpr int kBKBytes = 128;     // one swizzle row = 64 two-byte elements
 constexpr int kABytes = kBM * kBKBytes;          // 16 KB
 constexpr int kSubRows = 16;                     // rows per TMA box of the hidden cache
@@ -87,8 +88,8 @@ struct SmemAux {
   alignas(16) float q[kSubsPerTile][kHeadDim];   // per segment: query row of its request, pre-scaled
   float bk[kHeadDim];
   float bv[kHeadDim];
-  float sub_max[kSubsPerTile];
-  float sub_sum[kSubsPerTile];
+  float sub_max[kMaxHeadsPerTile][kSubsPerTile];   // per head of the tile (head sizes 64 / 32: 2 / 4 heads)
+  float sub_sum[kMaxHeadsPerTile][kSubsPerTile];
   alignas(16) float red_acc[kSubsPerTile][kHeadDim];   // written as float2
 };
 
@@ -402,10 +403,14 @@ __device__ __forceinline__ void epilogue_stage_inputs(SmemAux* aux, const Hidden
 
 // After the accumulator is ready.  `release()` is called once, when this thread's
 // last TMEM read has completed.
-template <typename T, int MODE, typename Release>
+template <typename T, int MODE, int NH, typename Release>
 __device__ __forceinline__ void epilogue_compute(SmemAux* aux, const HiddenParams& p, uint32_t t_row,
                                                  int tile, bool tile_ok, int head, int quarter,
                                                  int lane, int et, Release release) {
+  // `head` counts tiles of 128 K columns: NH heads of 128 / NH elements each, adjacent in W
+  // and in the query row, so that the loads and the accumulator look the same for every NH.
+  constexpr int kD = kHeadDim / NH;       // head size
+  constexpr int kChunks = 4 / NH;         // 32-column TMEM chunks per head
   const int row = quarter * 32 + lane;
   const int hcol = head * kHeadDim;
   uint32_t r[32];
@@ -447,62 +452,77 @@ __device__ __forceinline__ void epilogue_compute(SmemAux* aux, const HiddenParam
     valid = rec.y + (row & 15) < seq;
   }
   const float* qs = aux->q[my_seg >= 0 ? my_seg : 0];
-  // ---- scores: s = q . (K_row + b_k), already in the log2 domain ----
-  float s = 0.f;
+  // ---- scores: s = q . (K_row + b_k) per head, already in the log2 domain ----
+  float s[NH];
+#pragma unroll
+  for (int h = 0; h < NH; ++h) {
+    float acc = 0.f;
 #pragma unroll 1
-  for (int c = 0; c < 4; ++c) {
-    tmem_ld32(t_row + c * 32, r);
-    tmem_ld_wait();
+    for (int c = h * kChunks; c < (h + 1) * kChunks; ++c) {
+      tmem_ld32(t_row + c * 32, r);
+      tmem_ld_wait();
 #pragma unroll
-    for (int j = 0; j < 32; ++j)
-      s = fmaf(qs[c * 32 + j], __uint_as_float(r[j]) + aux->bk[c * 32 + j], s);
+      for (int j = 0; j < 32; ++j)
+        acc = fmaf(qs[c * 32 + j], __uint_as_float(r[j]) + aux->bk[c * 32 + j], acc);
+    }
+    s[h] = valid ? acc : -INFINITY;
+    // max over the 16 rows of the sub-block
+    float hm = s[h];
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) hm = fmaxf(hm, __shfl_xor_sync(0xffffffffu, hm, o));
+    if ((lane & 15) == 0) aux->sub_max[h][sub] = hm;
   }
-  s = valid ? s : -INFINITY;
-  // max over the 16 rows of the sub-block, then over the sub-blocks of the segment
-  float hm = s;
-#pragma unroll
-  for (int o = 8; o > 0; o >>= 1) hm = fmaxf(hm, __shfl_xor_sync(0xffffffffu, hm, o));
-  if ((lane & 15) == 0) aux->sub_max[sub] = hm;
   epi_barrier();
-  float mx = -INFINITY;
+  float pr[NH];
 #pragma unroll
-  for (int j = 0; j < kSubsPerTile; ++j)
-    if (aux->sub_seg[j] == my_seg) mx = fmaxf(mx, aux->sub_max[j]);
-  const float pr = valid ? exp2f(s - mx) : 0.f;
-  float hs = pr;
+  for (int h = 0; h < NH; ++h) {
+    // max over the sub-blocks of the segment
+    float mx = -INFINITY;
 #pragma unroll
-  for (int o = 8; o > 0; o >>= 1) hs += __shfl_xor_sync(0xffffffffu, hs, o);
-  if ((lane & 15) == 0) aux->sub_sum[sub] = hs;
+    for (int j = 0; j < kSubsPerTile; ++j)
+      if (aux->sub_seg[j] == my_seg) mx = fmaxf(mx, aux->sub_max[h][j]);
+    pr[h] = valid ? exp2f(s[h] - mx) : 0.f;
+    float hs = pr[h];
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) hs += __shfl_xor_sync(0xffffffffu, hs, o);
+    if ((lane & 15) == 0) aux->sub_sum[h][sub] = hs;
+  }
 
   // ---- weighted V rows, column sums over the 16 rows of the sub-block ----
-#pragma unroll 1
-  for (int c = 0; c < 4; ++c) {
-    tmem_ld32(t_row + kHeadDim + c * 32, r);
-    tmem_ld_wait();
-    float v[32];
 #pragma unroll
-    for (int j = 0; j < 32; ++j)
-      v[j] = valid ? pr * (__uint_as_float(r[j]) + aux->bv[c * 32 + j]) : 0.f;
-    half_warp_column_sum(v, lane);
-    *reinterpret_cast<float2*>(&aux->red_acc[sub][c * 32 + 2 * (lane & 15)]) = make_float2(v[0], v[1]);
+  for (int h = 0; h < NH; ++h) {
+    const float w = pr[h];
+#pragma unroll 1
+    for (int c = h * kChunks; c < (h + 1) * kChunks; ++c) {
+      tmem_ld32(t_row + kHeadDim + c * 32, r);
+      tmem_ld_wait();
+      float v[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        v[j] = valid ? w * (__uint_as_float(r[j]) + aux->bv[c * 32 + j]) : 0.f;
+      half_warp_column_sum(v, lane);
+      *reinterpret_cast<float2*>(&aux->red_acc[sub][c * 32 + 2 * (lane & 15)]) = make_float2(v[0], v[1]);
+    }
   }
   release();
   epi_barrier();
-  // ---- one partial per segment: thread et owns column et ----
+  // ---- one partial per segment and head: thread et owns column et of the tile ----
   const int n_seg = aux->n_seg;
+  const int my_h = et / kD;
   for (int sgm = 0; sgm < n_seg; ++sgm) {
     float a = 0.f, m_seg = -INFINITY, l_seg = 0.f;
 #pragma unroll
     for (int j = 0; j < kSubsPerTile; ++j)
       if (aux->sub_seg[j] == sgm) {
         a += aux->red_acc[j][et];
-        m_seg = fmaxf(m_seg, aux->sub_max[j]);
-        l_seg += aux->sub_sum[j];
+        m_seg = fmaxf(m_seg, aux->sub_max[my_h][j]);
+        l_seg += aux->sub_sum[my_h][j];
       }
     const int req = aux->seg_req[sgm];
+    // partial slots are laid out [slot][head][head size]; p.heads counts tiles of NH heads
     const int64_t slot = (int64_t)(p.part_offset[req] + tile - p.first_tile[req]) * p.heads + head;
     p.part_acc[slot * kHeadDim + et] = a;
-    if (et == 0) *reinterpret_cast<float2*>(p.part_ml + slot * 2) = make_float2(m_seg, l_seg);
+    if (et % kD == 0) *reinterpret_cast<float2*>(p.part_ml + (slot * NH + my_h) * 2) = make_float2(m_seg, l_seg);
   }
   epi_barrier();  // the segment tables and reduction buffers are rewritten by the next item
 }
@@ -590,7 +610,7 @@ __device__ __forceinline__ void tma_producer(const HiddenParams& p, SmemAux* aux
 }
 
 // ---- the kernel ---------------------------------------------------------------------
-template <typename T, int MODE>
+template <typename T, int MODE, int NH>
 __global__ void __launch_bounds__(kThreads, 1)
 hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_wk,
                    const __grid_constant__ CUtensorMap map_wv, const HiddenParams p) {
@@ -727,7 +747,7 @@ hidden_path_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(acc_empty), 0));
       };
-      epilogue_compute<T, MODE>(aux, p, t_row, tile, tile_ok, it.head, quarter, lane, et, release);
+      epilogue_compute<T, MODE, NH>(aux, p, t_row, tile, tile_ok, it.head, quarter, lane, et, release);
     }
   }
 
@@ -788,7 +808,7 @@ void raster_sizes(int* units, int* heads) {
 // Launch geometry: one CTA per SM, in pairs, as many pairs as the device keeps resident at
 // once.  Looked up once per kernel instantiation and device (the library assumes one calling
 // thread per process, like the reference's single-threaded worker).
-template <typename T, int MODE>
+template <typename T, int MODE, int NH>
 int launch_hidden(const CUtensorMap& mx, const CUtensorMap& mk, const CUtensorMap& mv,
                   HiddenParams p, cudaStream_t stream) {
   static int grid_for_device[64] = {0};
@@ -797,7 +817,7 @@ int launch_hidden(const CUtensorMap& mx, const CUtensorMap& mk, const CUtensorMa
   int dev = 0;
   APS_CUDA(cudaGetDevice(&dev));
   APS_REQUIRE(dev >= 0 && dev < 64, APS_ERR_CUDA, "device index %d out of range", dev);
-  auto kernel = hidden_path_kernel<T, MODE>;
+  auto kernel = hidden_path_kernel<T, MODE, NH>;
   constexpr size_t smem = smem_bytes();
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(kThreads);
@@ -834,11 +854,20 @@ struct HiddenArgs {
   int dtype;
 };
 
+// An accumulator tile holds 128 K columns and 128 V columns: one head of 128 elements, two
+// adjacent heads of 64 or four of 32 (their W rows and their slices of the query row are
+// adjacent, so only the softmax epilogue knows the difference).
+bool tensor_head_shape_ok(int heads, int head_size) {
+  return (head_size == 128 || head_size == 64 || head_size == 32) && heads > 0 &&
+         (heads * head_size) % kHeadDim == 0;
+}
+
 int check_hidden_args(const char* op, const HiddenArgs& a) {
   APS_REQUIRE(a.dtype == APS_F16 || a.dtype == APS_BF16, APS_ERR_UNSUPPORTED,
               "%s: the tensor-core re-projection supports fp16 and bf16 only (dtype %d)", op, a.dtype);
-  APS_REQUIRE(a.head_size == kHeadDim, APS_ERR_UNSUPPORTED,
-              "%s: the tensor-core re-projection supports head size 128 only (got %d)", op, a.head_size);
+  APS_REQUIRE(tensor_head_shape_ok(a.heads, a.head_size), APS_ERR_UNSUPPORTED,
+              "%s: the tensor-core re-projection takes head sizes 128, 64 and 32 with heads x head size a "
+              "multiple of 128 (got %d heads of %d)", op, a.heads, a.head_size);
   APS_REQUIRE(a.hidden_cache && a.w_k && a.w_v, APS_ERR_NULL_POINTER, "%s: null pointer", op);
   APS_REQUIRE(a.hidden_size > 0 && a.num_hidden_rows > 0 && a.hidden_row_stride >= a.hidden_size &&
                   a.w_stride >= a.hidden_size,
@@ -868,9 +897,10 @@ int enqueue_hybrid_attention(const HybridCall& c, cudaStream_t cs) {
   int st;
   HiddenArgs a{c.hidden_cache, c.w_k, c.b_k, c.w_v, c.b_v, s.heads, s.head_size, c.hidden_size,
                c.hidden_row_stride, c.num_hidden_rows, c.w_stride, s.dtype};
-  // fp16 / bf16 with head size 128 run on the tensor cores; fp32 and head sizes 32 / 64 run
-  // the CUDA-core re-projection (same work items, same partials)
-  const bool tensor_path = (s.dtype == APS_F16 || s.dtype == APS_BF16) && s.head_size == kHeadDim;
+  // fp16 / bf16 run on the tensor cores (head sizes 128 / 64 / 32 with heads x head size a
+  // multiple of 128); fp32 and the other head counts run the CUDA-core re-projection (same
+  // partials, one request per tile)
+  const bool tensor_path = (s.dtype == APS_F16 || s.dtype == APS_BF16) && tensor_head_shape_ok(s.heads, s.head_size);
   CUtensorMap mx, mk, mv;
   if (tensor_path) {
     if ((st = check_hidden_args("hybrid_decode_attention", a)) != APS_OK) return st;
@@ -878,7 +908,8 @@ int enqueue_hybrid_attention(const HybridCall& c, cudaStream_t cs) {
   } else {
     APS_REQUIRE(hidden_simt_supported(s.dtype, s.head_size), APS_ERR_UNSUPPORTED,
                 "hybrid_decode_attention: head size %d / dtype %d has no re-projection kernel "
-                "(tensor cores: fp16 or bf16 with head size 128; CUDA cores: head sizes 32, 64, 128)",
+                "(tensor cores: fp16 or bf16, head sizes 32 / 64 / 128 with heads x head size a multiple "
+                "of 128; CUDA cores: head sizes 32, 64, 128)",
                 s.head_size, s.dtype);
     APS_REQUIRE(c.hidden_cache && c.w_k && c.w_v, APS_ERR_NULL_POINTER, "hybrid_decode_attention: null pointer");
     APS_REQUIRE(c.hidden_size > 0 && c.hidden_row_stride >= c.hidden_size && c.w_stride >= c.hidden_size,
@@ -908,10 +939,18 @@ int enqueue_hybrid_attention(const HybridCall& c, cudaStream_t cs) {
   p.block_tables = c.block_tables; p.seq_lens = c.seq_lens;
   p.max_blocks_per_seq = s.max_blocks_per_seq; p.block_size = s.block_size;
   p.query_stride = s.query_stride; p.scale_log2 = s.scale * 1.4426950408889634f;
-  p.b_k = c.b_k; p.b_v = c.b_v; p.heads = s.heads; p.k_slabs = (c.hidden_size + 63) / 64;
+  // the kernel counts tiles of 128 K columns where the caller counts heads
+  p.b_k = c.b_k; p.b_v = c.b_v; p.heads = s.heads * s.head_size / kHeadDim; p.k_slabs = (c.hidden_size + 63) / 64;
   p.status = ws.plan + kPlanStatus;
-  st = s.dtype == APS_BF16 ? launch_hidden<__nv_bfloat16, kModeAttend>(mx, mk, mv, p, cs)
-                           : launch_hidden<__half, kModeAttend>(mx, mk, mv, p, cs);
+  const bool bf16 = s.dtype == APS_BF16;
+  switch (kHeadDim / s.head_size) {
+    case 1: st = bf16 ? launch_hidden<__nv_bfloat16, kModeAttend, 1>(mx, mk, mv, p, cs)
+                      : launch_hidden<__half, kModeAttend, 1>(mx, mk, mv, p, cs); break;
+    case 2: st = bf16 ? launch_hidden<__nv_bfloat16, kModeAttend, 2>(mx, mk, mv, p, cs)
+                      : launch_hidden<__half, kModeAttend, 2>(mx, mk, mv, p, cs); break;
+    default: st = bf16 ? launch_hidden<__nv_bfloat16, kModeAttend, 4>(mx, mk, mv, p, cs)
+                       : launch_hidden<__half, kModeAttend, 4>(mx, mk, mv, p, cs); break;
+  }
   if (st != APS_OK) return st;
   return launch_combine(ws, c.out, c.seq_lens, s, cs);
 }
@@ -977,11 +1016,12 @@ extern "C" int aps_kv_reprojection(void* kv, const void* x, const int32_t* block
   p.dense_a = dense ? 1 : 0;
   p.kv_out = kv; p.block_ids = block_ids; p.n_rows = n_rows; p.kv_stride = kv_stride;
   p.n_store_tiles = (int)((n_rows + kBM - 1) / kBM);
-  p.b_k = b_k; p.b_v = b_v; p.heads = num_heads; p.k_slabs = (hidden_size + 63) / 64;
+  // stored K | V rows are head-major, so heads smaller than 128 need nothing but the tile count
+  p.b_k = b_k; p.b_v = b_v; p.heads = num_heads * head_size / kHeadDim; p.k_slabs = (hidden_size + 63) / 64;
   p.status = status_word;
   cudaStream_t cs = (cudaStream_t)stream;
-  return dtype == APS_BF16 ? launch_hidden<__nv_bfloat16, kModeStore>(mx, mk, mv, p, cs)
-                           : launch_hidden<__half, kModeStore>(mx, mk, mv, p, cs);
+  return dtype == APS_BF16 ? launch_hidden<__nv_bfloat16, kModeStore, 1>(mx, mk, mv, p, cs)
+                           : launch_hidden<__half, kModeStore, 1>(mx, mk, mv, p, cs);
 }
 
 extern "C" int aps_selftest_bounded_wait(void* workspace, size_t workspace_bytes, long long budget_cycles,

@@ -647,6 +647,10 @@ def run_ours(args):
             line_extra[name] = blk
         status |= st.A.attention_status(st.workspace)
 
+    # ---- a plain device copy in the position of the HBM-bound kernels ----
+    if extras and cfg == 2 and tp == 1:
+        line_extra["hbm_copy_yardstick"] = copy_yardstick(st, peaks, max(5, K // 2))
+
     # ---- host-core baseline on a bounded sample (rank 0, N = 1 only) ----
     cpu_baseline = None
     if tp == 1 and not args.no_cpu_baseline:
@@ -792,6 +796,41 @@ def run_ours(args):
     print(json.dumps(line))
     if tp > 1:
         torch.distributed.destroy_process_group()
+
+
+def copy_yardstick(st, peaks, steps):
+    """`Tensor.copy_` of 512 MiB (the kind of copy the measured HBM peak was taken with) timed
+    alone and right behind the loaded decode step, where the K/V streaming and cache-write
+    kernels run: what a plain copy reaches at the step's power-capped clocks."""
+    n = 512 << 20
+    src = torch.empty(n, dtype=torch.uint8, device=st.w.query.device)
+    dst = torch.empty_like(src)
+
+    def timed(with_step):
+        for _ in range(3):
+            if with_step:
+                st.step()
+            dst.copy_(src)
+        t_end = time.perf_counter() + 0.3
+        while with_step and time.perf_counter() < t_end:
+            st.step()
+            torch.cuda.synchronize()
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        for e0, e1 in evs:
+            if with_step:
+                st.step()
+            e0.record()
+            dst.copy_(src)
+            e1.record()
+        torch.cuda.synchronize()
+        ms = sorted(e0.elapsed_time(e1) for e0, e1 in evs)[len(evs) // 2]
+        return round(2 * n / (ms * 1e-3) / 1e9, 1)
+
+    alone, behind = timed(False), timed(True)
+    return {"what": "torch copy_ of 512 MiB (library copy, yardstick only), read + write bytes, median of "
+                    f"{steps}: alone, and enqueued right behind each loaded decode step",
+            "alone_gbs": alone, "behind_the_step_gbs": behind, "peak": peaks["hbm_gbs"],
+            "alone_frac": round(alone / peaks["hbm_gbs"], 4), "behind_the_step_frac": round(behind / peaks["hbm_gbs"], 4)}
 
 
 def cache_write_block(st, ms, peaks, where):

@@ -230,8 +230,10 @@ int aps_paged_decode_attention_static(void* out, const void* query, const void* 
  * w_k / w_v: [H*D, hidden_size] row-major with row stride w_stride (the K and V
  * thirds of the fused QKV weight, lin.py:123-125); b_k / b_v: [H*D] or NULL.
  * num_hidden_rows is the number of addressable rows of hidden_cache
- * (2*NB*BS for the reference layout).  fp16 / bf16 with head_size 128 use the
- * tcgen05 path; other supported combinations use a CUDA-core re-projection.
+ * (2*NB*BS for the reference layout).  fp16 / bf16 with head_size 128, 64 or 32 and
+ * num_heads * head_size a multiple of 128 use the tcgen05 path (two heads of 64 or four
+ * of 32 share one accumulator tile); other supported combinations (fp32, other head
+ * counts) use a CUDA-core re-projection.
  * key_cache / value_cache may both be NULL for a batch without K/V-cached requests;
  * if such a batch does hold K/V-cached requests their output rows are zero and the
  * status word (aps_attention_status) reads 8.
@@ -252,7 +254,8 @@ int aps_hybrid_decode_attention(void* out, const void* query, const void* key_ca
 /*
  * The K/V re-projection on its own (opt.py:123 -> lin.py:123-130):
  *   kv[t, 0:HD] = X[t] W_k^T + b_k ; kv[t, HD:2HD] = X[t] W_v^T + b_v ,  t in [0, n_rows)
- * Same tensor-core main loop as the hybrid attention; fp16 / bf16, head_size 128.
+ * Same tensor-core main loop as the hybrid attention; fp16 / bf16, head_size 128, 64 or
+ * 32 with num_heads * head_size a multiple of 128.
  *   block_ids == NULL : X[t] is row t of x (the dense hidden_holder of opt.py:112-121);
  *   block_ids != NULL : X[t] is row block_ids[t / 16] * 16 + t % 16 of x, i.e. x is a
  *                       paged hidden cache read in 16-row blocks (int32 ids).

@@ -269,6 +269,57 @@ def test_hybrid_cuda_core_reprojection_shapes(dtype, heads, head_dim):
     assert_close(out, ref, f"CUDA-core re-projection {dtype} D{head_dim}", tol, tol)
 
 
+@pytest.mark.parametrize("dtype,heads,head_dim", [(torch.float16, 2, 64), (torch.bfloat16, 6, 64),
+                                                  (torch.float16, 4, 32), (torch.bfloat16, 12, 32)])
+def test_hybrid_tensor_core_reprojection_small_heads(dtype, heads, head_dim):
+    """Head sizes 64 and 32 with heads x head size a multiple of 128: two / four adjacent heads
+    share one accumulator tile of the tensor-core kernel, each with its own softmax."""
+    w = small_workload(dtype=dtype, heads=heads, head_dim=head_dim,
+                       lens=(5, 40, 17, 129, 300, 16, 128, 1, 260),
+                       hidden=(True, False, True, False, True, False, True, True, True))
+    ref = oracle_out(w)
+    out = gpu_hybrid(w.to("cuda"))
+    assert_close(out, ref, f"tensor-core re-projection {dtype} {heads} x {head_dim}")
+
+
+@pytest.mark.parametrize("name,heads,hidden,dtype", [("opt-125m", 12, 768, torch.float16),
+                                                     ("opt-350m", 16, 1024, torch.bfloat16),
+                                                     ("opt-1.3b", 32, 2048, torch.float16)])
+def test_hybrid_small_opt_models_head_size_64(name, heads, hidden, dtype):
+    """The OPT sizes with 64-element heads, in the 16-bit types the serving path runs."""
+    rng = np.random.default_rng(heads)
+    lens = [int(x) for x in rng.integers(1, 700, size=14)] + [2048, 16]
+    hid = [bool(b) for b in rng.random(len(lens)) < 0.5]
+    hid[-2] = True
+    w = make_decode_workload(LayerShape(name, heads, 64, hidden, dtype), lens, hid, seed=heads)
+    ref = oracle_out(w)
+    out = gpu_hybrid(w.to("cuda"))
+    assert_close(out, ref, f"{name} {dtype}")
+
+
+def test_cuda_core_and_tensor_core_reprojection_agree_head_size_64():
+    w = small_workload(heads=4, head_dim=64, lens=(70, 300, 129, 2), hidden=(True, True, False, True)).to("cuda")
+    tensor = gpu_hybrid(w).clone()
+    wk, bk, wv, bv = (t.float() for t in w.kv_weights())
+    simt = A.hybrid_decode_attention(w.query.float(), w.kv_cache.float(), w.hidden_cache.float(), wk, bk,
+                                     wv, bv, w.meta.private_block_tables, w.meta.seq_lens_tensor,
+                                     w.meta.cache_type, w.scale)
+    assert_close(simt, tensor.float(), "CUDA-core vs tensor-core path, head size 64", 5e-3, 5e-3)
+
+
+def test_kv_reprojection_head_size_64_and_32():
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(300, 256, generator=g).to(torch.float16)
+    wk = (torch.randn(256, 256, generator=g) * 0.05).to(torch.float16)
+    wv = (torch.randn(256, 256, generator=g) * 0.05).to(torch.float16)
+    bk = torch.randn(256, generator=g).to(torch.float16)
+    bv = torch.randn(256, generator=g).to(torch.float16)
+    ref = torch.cat([O.linear_fp32(x, wk, bk), O.linear_fp32(x, wv, bv)], dim=1)
+    for head_size in (64, 32):
+        out = A.kv_reprojection(x.cuda(), wk.cuda(), bk.cuda(), wv.cuda(), bv.cuda(), head_size)
+        assert_close(out, ref, f"kv_reprojection, head size {head_size}")
+
+
 def test_cuda_core_and_tensor_core_reprojection_agree():
     """The same fp16 values through the tcgen05 kernel (fp16 tensors) and through the
     CUDA-core kernel (the same values held as fp32 tensors)."""
@@ -515,6 +566,26 @@ def test_hybrid_ragged_batches_sweep(seed):
     assert_close(out, ref, f"sweep seed {seed}: B={batch} heads={heads} {dtype} lens={lens} hidden={hidden}")
     again = gpu_hybrid(dev)
     assert torch.equal(out, again), "two runs on the same inputs differ"
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_hybrid_ragged_batches_sweep_small_heads_tensor_path(seed):
+    """The ragged sweep on the tensor-core kernel with two (head size 64) and four (head
+    size 32) heads per accumulator tile."""
+    rng = np.random.default_rng(7200 + seed)
+    batch = int(rng.integers(1, 24))
+    lens = [int(rng.choice(EDGE_LENS)) if rng.random() < 0.7 else int(rng.integers(1, 700))
+            for _ in range(batch)]
+    hidden = [bool(b) for b in rng.random(batch) < (0.5, 1.0, 0.75)[seed % 3]]
+    head_dim = (64, 32)[seed % 2]
+    heads = (128 // head_dim) * int(rng.integers(1, 4))
+    dtype = (torch.float16, torch.bfloat16)[(seed // 2) % 2]
+    w = small_workload(dtype=dtype, heads=heads, head_dim=head_dim, lens=lens, hidden=hidden, seed=seed)
+    ref = oracle_out(w)
+    dev = w.to("cuda")
+    out = gpu_hybrid(dev)
+    assert_close(out, ref, f"sweep seed {seed}: B={batch} {heads} x {head_dim} {dtype} lens={lens} hidden={hidden}")
+    assert torch.equal(out, gpu_hybrid(dev)), "two runs on the same inputs differ"
 
 
 @pytest.mark.parametrize("seed", range(4))
