@@ -799,18 +799,21 @@ def run_ours(args):
 
 
 def copy_yardstick(st, peaks, steps):
-    """`Tensor.copy_` of 512 MiB (the kind of copy the measured HBM peak was taken with) timed
-    alone and right behind the loaded decode step, where the K/V streaming and cache-write
-    kernels run: what a plain copy reaches at the step's power-capped clocks."""
-    n = 512 << 20
-    src = torch.empty(n, dtype=torch.uint8, device=st.w.query.device)
+    """`Tensor.copy_` (the kind of copy the measured HBM peak was taken with) timed alone and
+    right behind the loaded decode step, where the K/V streaming and cache-write kernels run,
+    at two sizes: about the bytes configuration 3's cache writes move (2 x 480 MiB) and about
+    the bytes configuration 2's K/V path streams (2 x 1 GiB).  What a plain copy of that size
+    reaches at the step's power-capped clocks."""
+    dev = st.w.query.device
+    src = torch.empty(1 << 30, dtype=torch.uint8, device=dev)
     dst = torch.empty_like(src)
 
-    def timed(with_step):
+    def timed(n, with_step):
+        a, b = src[:n], dst[:n]
         for _ in range(3):
             if with_step:
                 st.step()
-            dst.copy_(src)
+            b.copy_(a)
         t_end = time.perf_counter() + 0.3
         while with_step and time.perf_counter() < t_end:
             st.step()
@@ -820,17 +823,20 @@ def copy_yardstick(st, peaks, steps):
             if with_step:
                 st.step()
             e0.record()
-            dst.copy_(src)
+            b.copy_(a)
             e1.record()
         torch.cuda.synchronize()
         ms = sorted(e0.elapsed_time(e1) for e0, e1 in evs)[len(evs) // 2]
         return round(2 * n / (ms * 1e-3) / 1e9, 1)
 
-    alone, behind = timed(False), timed(True)
-    return {"what": "torch copy_ of 512 MiB (library copy, yardstick only), read + write bytes, median of "
-                    f"{steps}: alone, and enqueued right behind each loaded decode step",
-            "alone_gbs": alone, "behind_the_step_gbs": behind, "peak": peaks["hbm_gbs"],
-            "alone_frac": round(alone / peaks["hbm_gbs"], 4), "behind_the_step_frac": round(behind / peaks["hbm_gbs"], 4)}
+    out = {"what": "torch copy_ (library copy, yardstick only), read + write bytes, median of "
+                   f"{steps}: alone, and enqueued right behind each loaded decode step", "peak": peaks["hbm_gbs"]}
+    for name, n in (("480_MiB", 480 << 20), ("1_GiB", 1 << 30)):
+        alone, behind = timed(n, False), timed(n, True)
+        out[name] = {"alone_gbs": alone, "behind_the_step_gbs": behind,
+                     "alone_frac": round(alone / peaks["hbm_gbs"], 4),
+                     "behind_the_step_frac": round(behind / peaks["hbm_gbs"], 4)}
+    return out
 
 
 def cache_write_block(st, ms, peaks, where):
