@@ -738,12 +738,27 @@ def run_ours(args):
         return
 
     roofline = dict(roof_hidden if work["t_hidden"] > 0 else roof_kv)
-    roofline["traffic"] = None
-    roofline["traffic_source"] = ("not captured for this launch: ncu captures of this kernel are taken on the "
-                                  "16-request case and its DRAM traffic does not "
-                                  "scale with the cached tokens alone (it depends on the work-order groups)")
-    roof_kv["traffic"] = int(1.02 * work["kv_attention_bytes"]) if work["t_kv"] else None
-    roof_kv["traffic_source"] = "ncu on the 16-request all-K/V case: 1.02 x the algorithmic bytes, scaled by the cached tokens"
+    # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum).  For the default workload
+    # (configuration 2, one GPU, all 256 requests) they were captured on this very launch: the two
+    # counters take one ncu pass, so nothing is saved or restored around the 5 GB the step holds.
+    default_workload = cfg == 2 and tp == 1 and args.batch is None and args.hidden_fraction is None
+    capture = ("`ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum --clock-control none -k regex:%s -s 3 -c 2 "
+               "python bench.py --steps 2 --warmup 3 --no-cpu-baseline --no-extras` (1 pass per launch), two launches: ")
+    if default_workload:
+        roofline["traffic"] = 7_440_000_000
+        roofline["traffic_source"] = (capture % "hidden_path" + "7.44 + 0.038 GB and 7.37 + 0.035 GB read + written, 6.9 x the "
+                                      "mandatory bytes (hidden rows and W once: 1.08 GB): W and the hidden rows are re-streamed "
+                                      "from HBM per round of work items, 0.9 TB/s = 14 % of the copy bandwidth")
+        roof_kv["traffic"] = 2_040_000_000
+        roof_kv["traffic_source"] = capture % "kv_attention_tma" + "2.02 + 0.02 GB, 1.02 x the algorithmic bytes"
+    else:
+        roofline["traffic"] = None
+        roofline["traffic_source"] = ("not captured for this workload (captured for the default one: configuration 2, one GPU); "
+                                      "the re-projection kernel's DRAM traffic depends on the work-order groups, not on the "
+                                      "cached tokens alone, so it is not scaled from another case")
+        roof_kv["traffic"] = int(1.02 * work["kv_attention_bytes"]) if work["t_kv"] else None
+        roof_kv["traffic_source"] = ("1.02 x the algorithmic bytes, the ratio ncu measured on configuration 2 and on the "
+                                     "16-request all-K/V case, scaled by the cached tokens")
     # the mixed step against its two lower bounds: every K/V byte at the measured copy bandwidth,
     # every re-projection FLOP at the measured sustained tensor rate; the step cannot beat the
     # larger of the two and would equal their sum if the two paths did not overlap at all
