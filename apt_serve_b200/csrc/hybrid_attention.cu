@@ -188,6 +188,11 @@ __device__ __forceinline__ uint64_t l2_policy_evict_last() {
   asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
   return p;
 }
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
 __device__ __forceinline__ uint64_t l2_policy_evict_normal() {
   uint64_t p;
   asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
@@ -287,7 +292,10 @@ struct HiddenParams {
   int* status;
 };
 
-struct Item { int unit, head; };   // unit = a pair of M tiles (2u, 2u + 1)
+struct Item {
+  int unit, head;     // unit = a pair of M tiles (2u, 2u + 1)
+  bool last_head;     // the block's last head: the unit's hidden rows are not read again in this head group
+};
 
 // Work order.  Heads are taken in groups of `rh`; inside a head group the units (tile
 // pairs) are taken in groups of `ru`; inside such a block the order is head-major.
@@ -307,6 +315,7 @@ __device__ __forceinline__ Item item_of(int i, int n_units, int heads, int ru, i
   Item it;
   it.head = hg * rh + hl;
   it.unit = ug * ru + within - hl * gm;
+  it.last_head = hl == hsz - 1;
   return it;
 }
 
@@ -557,15 +566,19 @@ __device__ __forceinline__ void tma_producer(const HiddenParams& p, SmemAux* aux
   const int j0 = prod > 0 ? (prod - 1) * 2 : kSubsPerTile;   // producer 0 owns no block slot
   const uint32_t sub_off = (uint32_t)(j0 * kSubBytes);
   const CUtensorMap* w_map = leader ? &map_wk : &map_wv;
-  // L2 eviction priorities: the W rows of the head group being worked on are re-read by every
-  // round of items and are asked to stay (evict_last); the hidden rows keep the normal priority
-  // (marking them evict_first evicted them before the group's other heads had read them: +2 %
-  // time; W evict_last alone: -1.6 % on configuration 2, four alternating runs each)
-  const uint64_t pol_w = l2_policy_evict_last(), pol_x = l2_policy_evict_normal();
+  // L2 eviction priorities.  The W rows of the head group being worked on are re-read by every
+  // round of items and are asked to stay (evict_last: -1.6 % time on configuration 2).  The
+  // hidden rows keep the normal priority while the block's other heads still have to read them
+  // and are marked evict_first on their last read of the head group (the block's last head):
+  // -10 % DRAM traffic at the same time.  Marking every read of them evict_first evicted them
+  // before the other heads had read them (+2 % time).
+  const uint64_t pol_w = l2_policy_evict_last(), pol_normal = l2_policy_evict_normal();
+  const uint64_t pol_first = l2_policy_evict_first();
   for (int i = first; i < n_items && ok; i += stride) {
     const Item it = item_of(i, n_units, p.heads, p.raster_units, p.raster_heads);
     const int tile = it.unit * 2 + (int)rank;
     const int n_sub = tile_n_sub<MODE>(p, tile, n_tiles);
+    const uint64_t pol_x = it.last_head ? pol_first : pol_normal;
     int sub_row[kSubsPerTile];
     tile_sub_rows<MODE>(p, n_sub > 0 ? tile : 0, n_sub, sub_row);
     // a dense X tile is one 128-row box (rows past the end are zero-filled and still
