@@ -537,6 +537,33 @@ def _varlen_prefill_attention(q, k, v, seq_start_loc, max_len, scale):
     return out
 
 
+def _prefix_prefill_attention(query, key_cache, value_cache, query_start_loc, seq_lens,
+                              block_tables, scale):
+    """Prefix-enabled prefill (aptserve_flash_attn.py:432-447): the new prompt tokens of each
+    sequence attend to the sequence's whole context, read through its block table from the
+    cache the step has just written; causal with the query rows aligned to the END of the
+    context.  Like the prefill attention without a prefix it stays a composition of library
+    calls (a gather by block id and scaled_dot_product_attention per sequence); the reference
+    calls flash_attn_varlen_func with ``block_table``."""
+    out = torch.empty_like(query)
+    bounds = query_start_loc.tolist()
+    bs = key_cache.shape[1]
+    for i, (a, b) in enumerate(zip(bounds[:-1], bounds[1:])):
+        n_q, n_ctx = b - a, int(seq_lens[i])
+        if n_q == 0:
+            continue
+        ids = block_tables[i, :(n_ctx + bs - 1) // bs].long()
+        k = key_cache.index_select(0, ids).flatten(0, 1)[:n_ctx]
+        v = value_cache.index_select(0, ids).flatten(0, 1)[:n_ctx]
+        pos = torch.arange(n_ctx, device=query.device)
+        mask = pos[None, :] <= (n_ctx - n_q + torch.arange(n_q, device=query.device))[:, None]
+        o = torch.nn.functional.scaled_dot_product_attention(
+            query[a:b].transpose(0, 1)[None], k.transpose(0, 1)[None], v.transpose(0, 1)[None],
+            attn_mask=mask, scale=scale)
+        out[a:b] = o[0].transpose(0, 1)
+    return out
+
+
 class FlashAttentionImpl:
     """Same constructor and ``forward`` signature as aptserve_flash_attn.py:251-299."""
 
@@ -625,7 +652,11 @@ class FlashAttentionImpl:
                     query, key, value, prefill_meta.seq_start_loc,
                     prefill_meta.max_prefill_seq_len, self.scale)
             else:
-                raise NotImplementedError("prefix-cached prefill is outside the hybrid-cache path")
+                # prefix-enabled attention over the K/V cache (aptserve_flash_attn.py:432-447)
+                assert prefill_meta.seq_lens is not None
+                output[:n_prefill] = _prefix_prefill_attention(
+                    query, key_cache, value_cache, prefill_meta.query_start_loc,
+                    prefill_meta.seq_lens, prefill_meta.block_tables, self.scale)
 
         if (decode_meta := m.decode_metadata) is not None:
             kc, vc = (key_cache, value_cache) if n_hidden == 0 else (shared_k, shared_v)

@@ -745,10 +745,11 @@ def run_ours(args):
     capture = ("`ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum --clock-control none -k regex:%s -s 3 -c 2 "
                "python bench.py --steps 2 --warmup 3 --no-cpu-baseline --no-extras` (1 pass per launch), two launches: ")
     if default_workload:
-        roofline["traffic"] = 7_440_000_000
-        roofline["traffic_source"] = (capture % "hidden_path" + "7.44 + 0.038 GB and 7.37 + 0.035 GB read + written, 6.9 x the "
+        roofline["traffic"] = 9_650_000_000
+        roofline["traffic_source"] = (capture % "hidden_path" + "9.61 + 0.037 GB and 9.47 + 0.033 GB read + written, 8.9 x the "
                                       "mandatory bytes (hidden rows and W once: 1.08 GB): W and the hidden rows are re-streamed "
-                                      "from HBM per round of work items, 0.9 TB/s = 14 % of the copy bandwidth")
+                                      "from HBM per round of work items, 1.2 TB/s = 18 % of the copy bandwidth; the figure moves "
+                                      "with the box (7.4 GB and 9.5 - 10.5 GB on two others), the kernel's time does not")
         roof_kv["traffic"] = 2_040_000_000
         roof_kv["traffic_source"] = capture % "kv_attention_tma" + "2.02 + 0.02 GB, 1.02 x the algorithmic bytes"
     else:

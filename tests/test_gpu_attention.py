@@ -476,6 +476,61 @@ def test_flash_attention_impl_kv_only_decode_and_prefill_write():
     assert torch.equal(kv.cpu().view(torch.uint8), kv_ref.view(torch.uint8))
 
 
+def test_flash_attention_impl_prefix_cached_prefill():
+    """Prefill whose prompts continue a cached prefix (aptserve_flash_attn.py:432-447): the new
+    tokens' K/V go to their slots, then each new token attends to the whole context through the
+    block table, causally aligned to the context's end."""
+    g = torch.Generator().manual_seed(11)
+    heads, d, bs, nb = 2, 64, 16, 32
+    ctx, new = [32, 48, 0], [10, 5, 20]
+    tables = [[3, 7, 9, 0], [1, 4, 12, 15], [20, 21, 0, 0]]
+    kv = (torch.randn(2, nb, bs, heads, d, generator=g) * 0.5).to(torch.float16)
+    n = sum(new)
+    q, k, v = ((torch.randn(n, heads * d, generator=g) * 0.5).to(torch.float16) for _ in range(3))
+    slots, starts = [], [0]
+    for c, m, t in zip(ctx, new, tables):
+        slots += [t[p // bs] * bs + p % bs for p in range(c, c + m)]
+        starts.append(starts[-1] + m)
+    seq_lens = [c + m for c, m in zip(ctx, new)]
+    # expected: fp32 attention over [cached prefix ; new tokens] per sequence
+    ref = torch.empty(n, heads * d)
+    kv_ref = kv.clone()
+    flat_k, flat_v = kv_ref[0].view(nb * bs, heads, d), kv_ref[1].view(nb * bs, heads, d)
+    flat_k[slots] = k.view(n, heads, d)
+    flat_v[slots] = v.view(n, heads, d)
+    scale = d ** -0.5
+    for i, (c, m, t) in enumerate(zip(ctx, new, tables)):
+        rows = [t[p // bs] * bs + p % bs for p in range(c + m)]
+        kk, vv = flat_k[rows].float(), flat_v[rows].float()
+        qq = q[starts[i]:starts[i + 1]].view(m, heads, d).float()
+        sc = torch.einsum("qhd,khd->hqk", qq, kk) * scale
+        mask = torch.arange(c + m)[None, :] <= (c + torch.arange(m))[:, None]
+        sc = sc.masked_fill(~mask[None], float("-inf"))
+        ref[starts[i]:starts[i + 1]] = torch.einsum("hqk,khd->qhd", sc.softmax(-1), vv).reshape(m, heads * d)
+    dev = "cuda"
+    empty = torch.zeros(0, dtype=torch.int64, device=dev)
+    cum = [0]
+    for s_ in seq_lens:
+        cum.append(cum[-1] + s_)
+    meta = A.FlashAttentionMetadata(
+        num_prefills=3, num_prefill_tokens=n, num_decode_tokens=0, num_hidden_cache_tokens=0,
+        num_tot_tokens=n, slot_mapping=torch.tensor(slots, dtype=torch.int64, device=dev),
+        slot_mapping_shared=empty, hidden_cache_use_tot=empty, kv_cache_use_tot=empty,
+        hidden_cache_use_input=empty, hidden_cache_store_tot=empty, hidden_holder_upd=empty,
+        hidden_holder_pull=empty, seq_lens=seq_lens,
+        seq_lens_tensor=torch.tensor(seq_lens, dtype=torch.int32, device=dev), max_query_len=max(new),
+        max_prefill_seq_len=max(seq_lens), max_decode_seq_len=0,
+        query_start_loc=torch.tensor(starts, dtype=torch.int32, device=dev),
+        seq_start_loc=torch.tensor(cum, dtype=torch.int32, device=dev),
+        context_lens_tensor=torch.tensor(ctx, dtype=torch.int32, device=dev),
+        block_tables=torch.tensor(tables, dtype=torch.int32, device=dev), use_cuda_graph=False)
+    impl = A.FlashAttentionImpl(heads, d, scale, heads, None, None, "auto")
+    kv_dev = kv.to(dev)
+    out = impl.forward(q.to(dev), k.to(dev), v.to(dev), kv_dev, None, meta)
+    assert torch.equal(kv_dev.cpu().view(torch.uint8), kv_ref.view(torch.uint8))
+    assert_close(out, ref, "prefix-cached prefill")
+
+
 def test_opt_attention_prefill_fused_write_matches_literal():
     """A prefill batch with hidden-designated prompts through both forms of OPTAttention:
     same cache contents bit for bit, same attention output."""
