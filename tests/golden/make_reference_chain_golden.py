@@ -1,0 +1,77 @@
+"""Generates ``tests/golden/reference_chain_decode.npz``: outputs of the REFERENCE's own decode
+op chain, run on a B200 with the kernels the reference runs -- its ``mixed_cache.cu``
+compiled unmodified (``oracle/_ref``), ``torch.nn.functional.linear`` (cuBLAS) for the
+``kv_only`` projection, vLLM's ``reshape_and_cache_flash`` and flash-attention paged
+decode (aptserve_opt.py:106-124, aptserve_flash_attn.py:356-387, 452-473).
+
+The inputs are seeded workloads that the CPU can rebuild bit for bit, so the file holds only
+the cases' parameters and the chain's outputs.  ``tests/test_golden.py`` checks the CPU
+oracle against them without a GPU.  Needs a GPU, the built ``oracle/_ref`` extension and
+vLLM's flash-attention; run from the repository root:
+
+    python tests/golden/make_reference_chain_golden.py [output.npz]
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+
+from apt_serve_b200.workloads import LayerShape, make_decode_workload  # noqa: E402
+from oracle.literal_chain_gpu import LiteralChain  # noqa: E402
+
+OUT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_chain_decode.npz")
+
+# name -> (heads, head size, hidden size, sequence lengths, hidden-cached flags, seed, projected K/V cache)
+CASES = {
+    # every request hidden-cached: gather, GEMM, scatter into the shared cache, paged attention
+    "all_hidden": (4, 128, 512, [5, 129, 300, 16, 1, 700], [True] * 6, 33, False),
+    # a mixed batch inside the envelope where the reference's mixed_kv_to_cache index is the
+    # intended one (hidden tokens <= 2 x K/V requests)
+    "mixed": (4, 128, 512, [30, 17, 33] + [int(x) for x in np.random.default_rng(1).integers(1, 400, size=40)],
+              [True] * 3 + [False] * 40, 21, True),
+    # K/V-cached requests only: the private cache through the third-party paged attention
+    "kv_only": (4, 128, 512, [1, 15, 16, 17, 127, 128, 129, 300, 1000, 2048], [False] * 10, 5, False),
+}
+
+
+def build_case(case):
+    """The case's workload, drawn on the CPU (the random stream of a CUDA generator differs)."""
+    heads, d, e, lens, hid, seed, proj = CASES[case]
+    shape = LayerShape("golden", heads, d, e, torch.float16)
+    return make_decode_workload(shape, list(lens), list(hid), seed=seed, device="cpu",
+                                with_shared_cache=any(hid), kv_from_projection=proj)
+
+
+def main(path):
+    chain, why = LiteralChain.create()
+    if chain is None:
+        raise SystemExit(f"reference chain unavailable: {why}")
+    out = {}
+    for case in CASES:
+        w = build_case(case).to("cuda")
+        if any(w.use_hidden):
+            hd = w.heads * w.shape.head_dim
+            y = chain.hybrid_decode_layer(w.hidden_states, w.query, w.qkv_weight[hd:], w.qkv_bias[hd:],
+                                          w.kv_cache, w.shared_cache, w.meta, w.scale)
+            m = w.meta
+            slots = m.slot_mapping[m.hidden_cache_store_tot]
+            rows = w.kv_cache.view(-1, w.kv_cache.stride(2))[slots]
+            out[case + "/new_hidden_rows"] = rows.cpu().numpy().view(np.uint16)
+        else:
+            y = chain.decode_attention(w.query, w.kv_cache[0], w.kv_cache[1], w.meta.block_tables,
+                                       w.meta.seq_lens_tensor, w.scale)
+        torch.cuda.synchronize()
+        out[case + "/out"] = y.cpu().numpy().view(np.uint16)      # fp16 bits
+        out[case + "/seq_lens"] = np.asarray(w.seq_lens, dtype=np.int32)
+    out["attention_name"] = np.asarray(chain.attention_name)
+    out["gpu"] = np.asarray(torch.cuda.get_device_name(0))
+    np.savez_compressed(path, **out)
+    print("wrote", path, {k: v.shape for k, v in out.items()})
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else OUT)

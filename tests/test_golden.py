@@ -1,6 +1,13 @@
-"""Known-answer vectors of configuration 1 (tests/golden/config1_layer_step.npz, made by
-tests/golden/make_golden.py from the CPU oracle): the oracle and the workload generator
-must still reproduce them, and the GPU path must hit them."""
+"""Known-answer vectors.
+
+tests/golden/config1_layer_step.npz (made by tests/golden/make_golden.py from the CPU oracle,
+configuration 1): the oracle and the workload generator must still reproduce them, and the
+GPU path must hit them.
+
+tests/golden/reference_chain_decode.npz (made by tests/golden/make_reference_chain_golden.py
+on a B200 from the REFERENCE's own op chain: its mixed_cache.cu unmodified, cuBLAS, vLLM's
+cache write and flash-attention paged decode): the CPU oracle must agree with what the
+reference computed, and so must this package's kernels."""
 import os
 
 import numpy as np
@@ -67,3 +74,86 @@ def test_gpu_layer_step_hits_the_golden_output():
     new_slots = m.slot_mapping[m.hidden_holder_upd][m.cache_type != 0]
     written = O.flat_rows(w.kv_cache.cpu())[new_slots.cpu()][:, :8].numpy()
     assert np.array_equal(written, g["written_rows"])
+
+
+# --------------------------------------------------------------------------- #
+# outputs of the reference's own op chain, recorded on a B200
+# --------------------------------------------------------------------------- #
+CHAIN_GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_chain_decode.npz")
+
+
+def _chain_cases():
+    import importlib.util
+    spec = importlib.util.spec_from_file_location(
+        "make_reference_chain_golden",
+        os.path.join(os.path.dirname(CHAIN_GOLDEN), "make_reference_chain_golden.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def _fp16(a: np.ndarray) -> torch.Tensor:
+    return torch.from_numpy(a.view(np.float16).copy())
+
+
+def _close(x: torch.Tensor, ref: torch.Tensor, tol: float, what: str):
+    err = (x.float() - ref.float()).abs()
+    bound = tol + tol * ref.float().abs()
+    assert bool((err <= bound).all()), f"{what}: max abs err {err.max().item():.3e}"
+
+
+@pytest.mark.parametrize("case", ["all_hidden", "mixed", "kv_only"])
+def test_oracle_matches_the_recorded_reference_chain(case):
+    """The CPU oracle against what the reference's own kernels produced for the same seeded
+    inputs (mixed_cache.cu unmodified + cuBLAS + vLLM's cache write and flash-attention paged
+    decode, recorded by tests/golden/make_reference_chain_golden.py on a B200).  Tolerance:
+    |x - ref| <= 4e-3 + 4e-3 |ref| (fp32 oracle with K/V rounded to fp16 like the GEMM's
+    output, against fp16 tensor-core arithmetic); rows that are plain copies are bit-exact."""
+    g = np.load(CHAIN_GOLDEN)
+    w = _chain_cases().build_case(case)
+    assert np.array_equal(g[case + "/seq_lens"], np.asarray(w.seq_lens, dtype=np.int32))
+    ref = _fp16(g[case + "/out"])
+    if case == "kv_only":
+        out = O.paged_decode_attention(w.query, w.kv_cache[0], w.kv_cache[1], w.meta.block_tables,
+                                       w.meta.seq_lens_tensor, w.scale)
+        _close(out, ref, 4e-3, "oracle vs recorded paged decode")
+        return
+    m = w.meta
+    O.hidden_to_cache(w.hidden_states, w.kv_cache, m.slot_mapping, m.hidden_cache_use_input,
+                      m.hidden_cache_store_tot)
+    slots = m.slot_mapping[m.hidden_cache_store_tot]
+    assert torch.equal(O.flat_rows(w.kv_cache)[slots].view(torch.int16),
+                       torch.from_numpy(g[case + "/new_hidden_rows"].view(np.int16).copy()))
+    wk, bk, wv, bv = w.kv_weights()
+    out = O.hybrid_decode_attention(w.query, w.kv_cache, w.kv_cache, wk, bk, wv, bv,
+                                    m.private_block_tables, m.seq_lens_tensor, m.cache_type, w.scale,
+                                    torch.float16)
+    rows = [r for r, h in enumerate(w.use_hidden) if h]    # the chain's rows of hidden requests
+    _close(out[rows], ref[rows], 4e-3, f"oracle vs recorded chain ({case})")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", ["all_hidden", "mixed", "kv_only"])
+def test_gpu_kernels_match_the_recorded_reference_chain(case):
+    """This package's kernels against the recorded outputs of the reference's chain (needs
+    none of the third-party kernels on the box).  |x - ref| <= 2e-2 + 2e-2 |ref|."""
+    from apt_serve_b200 import attention as A
+    g = np.load(CHAIN_GOLDEN)
+    w = _chain_cases().build_case(case).to("cuda")
+    ref = _fp16(g[case + "/out"])
+    if case == "kv_only":
+        out = A.paged_decode_attention(w.query, w.kv_cache[0], w.kv_cache[1], w.meta.block_tables,
+                                       w.meta.seq_lens_tensor, w.scale)
+        _close(out.cpu(), ref, 2e-2, "paged decode vs recorded chain")
+        return
+    wk, bk, wv, bv = w.kv_weights()
+    out = A.decode_layer_step(w.query, w.hidden_states, w.new_key, w.new_value, w.kv_cache, w.hidden_cache,
+                              wk, bk, wv, bv, w.meta.private_block_tables, w.meta.seq_lens_tensor,
+                              w.meta.cache_type, w.scale)
+    A.raise_on_device_status()
+    m = w.meta
+    slots = m.slot_mapping[m.hidden_cache_store_tot]
+    assert torch.equal(O.flat_rows(w.kv_cache)[slots].cpu().view(torch.int16),
+                       torch.from_numpy(g[case + "/new_hidden_rows"].view(np.int16).copy()))
+    rows = [r for r, h in enumerate(w.use_hidden) if h]
+    _close(out.cpu()[rows], ref[rows], 2e-2, f"fused layer-step vs recorded chain ({case})")
