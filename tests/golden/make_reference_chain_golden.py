@@ -46,11 +46,57 @@ def build_case(case):
                                 with_shared_cache=any(hid), kv_from_projection=proj)
 
 
+# The three mixed_cache_ops of the reference build on their own, bit for bit.  "outside": more
+# hidden tokens than twice the K/V requests, where the kernel's `blockIdx.x % (2 * n_kv)` index
+# (mixed_cache.cu:88) re-reads the first 2 * n_kv hidden tokens instead of walking all of them
+# (every index it forms stays inside its tensor as long as there is at least one K/V request).
+OPS_CASES = {
+    "ops_inside": ([3, 40, 17, 4, 64, 9], [True, False, False, True, False, False]),
+    "ops_outside": ([3, 40, 17, 4, 64, 9], [True, True, False, True, False, True]),
+}
+
+
+def build_ops_case(case):
+    lens, hid = OPS_CASES[case]
+    shape = LayerShape("golden-ops", 1, 32, 32, torch.float16)
+    w = make_decode_workload(shape, lens, hid, seed=3, device="cpu", with_shared_cache=True)
+    g = torch.Generator().manual_seed(1)
+    n = w.meta.num_tot_tokens
+    key = torch.randn(n, 1, 32, generator=g).to(torch.float16)
+    value = torch.randn(n, 1, 32, generator=g).to(torch.float16)
+    holder = torch.randn(n, 32, generator=g).to(torch.float16)
+    return w, key, value, holder
+
+
+def record_ops(out):
+    from oracle import build_ref
+    ext = build_ref.load()
+    for case in OPS_CASES:
+        w, key, value, holder = build_ops_case(case)
+        assert w.meta.kv_cache_use_tot.numel() > 0
+        d, m = w.to("cuda"), None
+        m = d.meta
+        hold = holder.cuda()
+        ext.hidden_to_cache(d.hidden_states, d.kv_cache, m.slot_mapping, m.hidden_cache_use_input,
+                            m.hidden_cache_store_tot)
+        torch.cuda.synchronize()
+        ext.cache_to_hidden(hold, d.kv_cache, m.slot_mapping, m.hidden_cache_use_tot)
+        torch.cuda.synchronize()
+        ext.mixed_kv_to_cache(key.cuda(), value.cuda(), d.kv_cache[0], d.kv_cache[1], d.shared_cache[0],
+                              d.shared_cache[1], m.slot_mapping, m.slot_mapping_shared, m.kv_cache_use_tot,
+                              m.hidden_cache_use_tot)
+        torch.cuda.synchronize()
+        out[case + "/kv_cache"] = d.kv_cache.cpu().numpy().view(np.uint16)
+        out[case + "/shared_cache"] = d.shared_cache.cpu().numpy().view(np.uint16)
+        out[case + "/hidden_holder"] = hold.cpu().numpy().view(np.uint16)
+
+
 def main(path):
     chain, why = LiteralChain.create()
     if chain is None:
         raise SystemExit(f"reference chain unavailable: {why}")
     out = {}
+    record_ops(out)
     for case in CASES:
         w = build_case(case).to("cuda")
         if any(w.use_hidden):

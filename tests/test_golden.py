@@ -157,3 +157,39 @@ def test_gpu_kernels_match_the_recorded_reference_chain(case):
                        torch.from_numpy(g[case + "/new_hidden_rows"].view(np.int16).copy()))
     rows = [r for r, h in enumerate(w.use_hidden) if h]
     _close(out.cpu()[rows], ref[rows], 2e-2, f"fused layer-step vs recorded chain ({case})")
+
+
+@pytest.mark.parametrize("case", ["ops_inside", "ops_outside"])
+def test_oracle_cache_ops_match_the_recorded_reference_build(case):
+    """hidden_to_cache, cache_to_hidden and mixed_kv_to_cache of the oracle against what the
+    reference's own extension (mixed_cache.cu compiled unmodified) wrote for the same seeded
+    inputs, bit for bit.  "ops_outside" has more hidden tokens than twice the K/V requests:
+    there the reference re-reads the first 2 * n_kv hidden tokens (mixed_cache.cu:88), which the
+    oracle restates with literal_index=True."""
+    g = np.load(CHAIN_GOLDEN)
+    w, key, value, holder = _chain_cases().build_ops_case(case)
+    m = w.meta
+    inside = m.slot_mapping_shared.numel() <= 2 * m.kv_cache_use_tot.numel()
+    assert inside == (case == "ops_inside")
+    kv, shared = w.kv_cache, w.shared_cache
+    O.hidden_to_cache(w.hidden_states, kv, m.slot_mapping, m.hidden_cache_use_input, m.hidden_cache_store_tot)
+    O.cache_to_hidden(holder, kv, m.slot_mapping, m.hidden_cache_use_tot)
+    O.mixed_kv_to_cache(key, value, kv[0], kv[1], shared[0], shared[1], m.slot_mapping,
+                        m.slot_mapping_shared, m.kv_cache_use_tot, m.hidden_cache_use_tot,
+                        literal_index=True)
+
+    def same(t, name):
+        return np.array_equal(t.contiguous().view(torch.int16).numpy().view(np.uint16), g[case + "/" + name])
+
+    assert same(kv, "kv_cache"), "private cache differs from the reference build's"
+    assert same(holder, "hidden_holder"), "gathered hidden rows differ from the reference build's"
+    assert same(shared, "shared_cache"), "shared cache differs from the reference build's"
+    if inside:
+        # inside the envelope the literal index is the intended one
+        w2, key2, value2, _ = _chain_cases().build_ops_case(case)
+        m2 = w2.meta
+        O.hidden_to_cache(w2.hidden_states, w2.kv_cache, m2.slot_mapping, m2.hidden_cache_use_input,
+                          m2.hidden_cache_store_tot)
+        O.mixed_kv_to_cache(key2, value2, w2.kv_cache[0], w2.kv_cache[1], w2.shared_cache[0], w2.shared_cache[1],
+                            m2.slot_mapping, m2.slot_mapping_shared, m2.kv_cache_use_tot, m2.hidden_cache_use_tot)
+        assert torch.equal(w2.shared_cache.view(torch.int16), shared.view(torch.int16))
