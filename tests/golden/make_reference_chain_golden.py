@@ -91,12 +91,35 @@ def record_ops(out):
         out[case + "/hidden_holder"] = hold.cpu().numpy().view(np.uint16)
 
 
+def build_cache_write_case():
+    """Inputs of the recorded `reshape_and_cache_flash` call: strided key / value rows (views
+    of a fused QKV tensor, as in the model), slots in random order, some of them -1."""
+    g = torch.Generator().manual_seed(7)
+    heads, d, bs, nb, t = 2, 32, 16, 12, 50
+    qkv = torch.randn(t, 3 * heads * d, generator=g).to(torch.float16)
+    key = qkv[:, heads * d:2 * heads * d].view(t, heads, d)
+    value = qkv[:, 2 * heads * d:].view(t, heads, d)
+    slots = torch.randperm(nb * bs, generator=g)[:t].to(torch.int64)
+    slots[::7] = -1
+    cache = torch.randn(2, nb, bs, heads, d, generator=g).to(torch.float16)
+    return key, value, slots, cache
+
+
+def record_cache_write(out, chain):
+    key, value, slots, cache = build_cache_write_case()
+    c = cache.cuda()
+    chain.reshape_and_cache(key.cuda(), value.cuda(), c[0], c[1], slots.cuda())
+    torch.cuda.synchronize()
+    out["reshape_and_cache_flash/cache"] = c.cpu().numpy().view(np.uint16)
+
+
 def main(path):
     chain, why = LiteralChain.create()
     if chain is None:
         raise SystemExit(f"reference chain unavailable: {why}")
     out = {}
     record_ops(out)
+    record_cache_write(out, chain)
     for case in CASES:
         w = build_case(case).to("cuda")
         if any(w.use_hidden):

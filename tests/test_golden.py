@@ -193,3 +193,23 @@ def test_oracle_cache_ops_match_the_recorded_reference_build(case):
         O.mixed_kv_to_cache(key2, value2, w2.kv_cache[0], w2.kv_cache[1], w2.shared_cache[0], w2.shared_cache[1],
                             m2.slot_mapping, m2.slot_mapping_shared, m2.kv_cache_use_tot, m2.hidden_cache_use_tot)
         assert torch.equal(w2.shared_cache.view(torch.int16), shared.view(torch.int16))
+
+
+def test_oracle_reshape_and_cache_flash_matches_the_recorded_vllm_op():
+    """The oracle's paged K/V scatter against what vLLM's `_custom_ops.reshape_and_cache_flash`
+    wrote (the third-party op behind aptserve_flash_attn.py:338-345): strided inputs, -1 slots."""
+    g = np.load(CHAIN_GOLDEN)
+    key, value, slots, cache = _chain_cases().build_cache_write_case()
+    O.reshape_and_cache_flash(key, value, cache[0], cache[1], slots)
+    assert np.array_equal(cache.view(torch.int16).numpy().view(np.uint16), g["reshape_and_cache_flash/cache"])
+
+
+@pytest.mark.gpu
+def test_gpu_reshape_and_cache_flash_matches_the_recorded_vllm_op():
+    from apt_serve_b200 import ops
+    g = np.load(CHAIN_GOLDEN)
+    key, value, slots, cache = _chain_cases().build_cache_write_case()
+    c = cache.cuda()
+    ops.reshape_and_cache_flash(key.cuda(), value.cuda(), c[0], c[1], slots.cuda(), "auto")
+    torch.cuda.synchronize()
+    assert np.array_equal(c.cpu().view(torch.int16).numpy().view(np.uint16), g["reshape_and_cache_flash/cache"])
