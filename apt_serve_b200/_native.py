@@ -54,6 +54,7 @@ PROTOTYPES = {
     "aps_decode_layer_step": (c_int, [c_void_p] * 15 + [c_int] * 6 + [c_int64] * 9 +
                               [c_float, c_void_p, c_size_t, c_int, c_void_p]),
     "aps_attention_status": (c_int, [c_void_p, c_void_p, c_void_p]),
+    "aps_reprojection_cycles": (c_int, [c_void_p, c_void_p, c_void_p]),
     "aps_cache_ops_status": (c_int, [c_void_p, c_void_p]),
     "aps_selftest_bounded_wait": (c_int, [c_void_p, c_size_t, ctypes.c_longlong, c_void_p] + [c_int] * 5 +
                                   [c_int64, c_int, c_void_p]),

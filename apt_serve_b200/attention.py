@@ -56,6 +56,18 @@ def attention_status(workspace: torch.Tensor) -> int:
     return host.value
 
 
+def reprojection_cycles(workspace: torch.Tensor) -> int:
+    """SM clock cycles CTA 0 of the re-projection kernel spent in the last hybrid call that
+    used ``workspace``.  Synchronises the current stream."""
+    import ctypes
+    host = ctypes.c_ulonglong(0)
+    dev = workspace.device
+    with torch.cuda.device(dev):
+        N.check(N.lib().aps_reprojection_cycles(N.ptr(workspace), ctypes.addressof(host),
+                                                N.current_stream(dev)))
+    return host.value
+
+
 def raise_on_device_status(workspace: Optional[torch.Tensor] = None,
                            device: Optional[torch.device] = None) -> None:
     """Raise ``RuntimeError`` if the last attention call on ``workspace`` (default: the

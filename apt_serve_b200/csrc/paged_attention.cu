@@ -869,6 +869,16 @@ extern "C" int aps_attention_status(const void* workspace, int* host_status, voi
   return APS_OK;
 }
 
+extern "C" int aps_reprojection_cycles(const void* workspace, unsigned long long* host_cycles, void* stream) {
+  APS_REQUIRE(workspace != nullptr && host_cycles != nullptr, APS_ERR_NULL_POINTER,
+              "reprojection_cycles: null pointer");
+  const unsigned long long* word =
+      reinterpret_cast<const unsigned long long*>(static_cast<const int*>(workspace) + kPlanStatsWord) + 8;
+  APS_CUDA(cudaMemcpyAsync(host_cycles, word, sizeof(unsigned long long), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  APS_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+  return APS_OK;
+}
+
 // ---- decode attention for callers that cannot allocate -----------------------------
 // The scratch of aps_paged_decode_attention_static lives in this module's image: a
 // fixed array in device memory that every GPU which loads the library holds until the

@@ -596,6 +596,8 @@ def run_ours(args):
     ms_per_step = res["ms_per_step"]
     status = st.A.attention_status(st.workspace)
     roof_hidden, roof_kv = kernel_rooflines(work, res, peaks)
+    if work["t_hidden"] > 0 and shape.dtype != torch.float32:
+        roof_hidden.update(tensor_cycle_block(st, shape, lens, hid, tp))
 
     out_shape = (B, shape.hidden) if tp > 1 else tuple(w.query.shape)
     e2e = EndToEnd(st, dev, tp, out_shape, shape.dtype)
@@ -812,6 +814,25 @@ def run_ours(args):
     print(json.dumps(line))
     if tp > 1:
         torch.distributed.destroy_process_group()
+
+
+def tensor_cycle_block(st, shape, lens, hid, tp):
+    """The re-projection kernel's own cycle count (CTA 0, last launch) against the cycles the
+    tensor cores need for its tiles: a pair of 128-row tiles x 128 K + 128 V columns costs
+    512 SM cycles per 64-element slab of the hidden size (four M256 N256 K16 instructions), the
+    74 CTA pairs take the tile pairs x heads round robin.  A utilisation figure that does not
+    depend on a sampled clock."""
+    sms = torch.cuda.get_device_properties(st.w.query.device).multi_processor_count
+    subs = sum((s + 15) // 16 for s, h in zip(lens, hid) if h)      # 16-row blocks, packed 8 per tile
+    tiles = (subs + 7) // 8
+    units = (tiles + 1) // 2
+    items = units * (shape.num_heads // tp) * shape.head_dim // 128
+    rounds = -(-items // (sms // 2))
+    need = rounds * (-(-shape.hidden // 64)) * 512
+    cycles = st.A.reprojection_cycles(st.workspace)
+    return {"sm_cycles_cta0": cycles, "tensor_bound_cycles": need,
+            "tensor_cycle_fraction": round(need / cycles, 4) if cycles else None,
+            "work_items_per_cta_pair": round(items / (sms // 2), 2)}
 
 
 def copy_yardstick(st, peaks, steps):

@@ -307,6 +307,15 @@ int aps_decode_layer_step(void* out, const void* query, const void* hidden_state
 int aps_attention_status(const void* workspace, int* host_status, void* stream);
 
 /*
+ * SM clock cycles CTA 0 of the tensor-core re-projection kernel spent in the last hybrid
+ * call that used `workspace` (two clock reads per launch, always recorded).  Against the
+ * cycles the tensor cores need for the call's tiles (512 per 64-element slab of a 256 x 256
+ * tile pair) this is the kernel's tensor-pipe utilisation, independent of sampled clocks.
+ * Synchronises `stream`.  No reference counterpart.
+ */
+int aps_reprojection_cycles(const void* workspace, unsigned long long* host_cycles, void* stream);
+
+/*
  * Status of the bulk-copy cache writes on the current device: 0, or 1 once a bounded
  * wait on a bulk load ran out (the launch then stopped copying).  Synchronises `stream`.
  */
