@@ -649,9 +649,11 @@ def run_ours(args):
             line_extra[name] = blk
         status |= st.A.attention_status(st.workspace)
 
-    # ---- a plain device copy in the position of the HBM-bound kernels ----
+    # ---- a plain device copy in the position of the HBM-bound kernels, and the library GEMM the
+    # tensor peak was measured with, on THIS box in THIS run ----
     if extras and cfg == 2 and tp == 1:
         line_extra["hbm_copy_yardstick"] = copy_yardstick(st, peaks, max(5, K // 2))
+        line_extra["gemm_yardstick"] = gemm_yardstick(timer, peaks, roof_hidden)
 
     # ---- host-core baseline on a bounded sample (rank 0, N = 1 only) ----
     cpu_baseline = None
@@ -833,6 +835,26 @@ def tensor_cycle_block(st, shape, lens, hid, tp):
     return {"sm_cycles_cta0": cycles, "tensor_bound_cycles": need,
             "tensor_cycle_fraction": round(need / cycles, 4) if cycles else None,
             "work_items_per_cta_pair": round(items / (sms // 2), 2)}
+
+
+def gemm_yardstick(timer, peaks, roof_hidden):
+    """The measured tensor peak is `torch.matmul` on 8192^3 bf16 (cuBLAS) in a seconds-long loop
+    on one B200 of the pool; the power cap makes that figure move with the box.  The same GEMM
+    (fp16, like the step) run here as a loaded loop, so that the re-projection kernel's TFLOP/s
+    can be read against what the library reaches on this box in this run."""
+    n = 8192
+    dev = torch.device("cuda", torch.cuda.current_device())
+    a = torch.randn(n, n, device=dev, dtype=torch.float16)
+    b = torch.randn(n, n, device=dev, dtype=torch.float16)
+    c = torch.empty(n, n, device=dev, dtype=torch.float16)
+    r = timer.run(lambda: torch.matmul(a, b, out=c), 60, 5, preload_s=0.5)
+    tflops = 2 * n ** 3 / (r["ms_per_step"] * 1e-3) / 1e12
+    out = {"what": "torch.matmul 8192 x 8192 x 8192 fp16 (cuBLAS, yardstick only), 60 back-to-back calls after "
+                   "half a second of the same", "tflops": round(tflops, 1), "ms_per_call": round(r["ms_per_step"], 4),
+           "measured_sustained_peak": peaks["tflops_sustained"], "clocks": r.get("clocks")}
+    if roof_hidden.get("achieved"):
+        out["reprojection_kernel_over_this_gemm"] = round(roof_hidden["achieved"] / tflops, 4)
+    return out
 
 
 def copy_yardstick(st, peaks, steps):

@@ -358,6 +358,22 @@ def test_kv_requests_without_kv_cache_set_the_status_and_give_zero_rows():
     A.raise_on_device_status(ws)
 
 
+def test_reprojection_cycle_count_is_at_least_the_tensor_bound():
+    """aps_reprojection_cycles after a hybrid call: CTA 0's cycles cover at least the 512 cycles
+    per 64-element slab its tile pairs need on the tensor cores, and not absurdly more."""
+    w = make_config_workload(5, device="cuda", batch=8, hidden_fraction=1.0)
+    out = gpu_hybrid(w)
+    assert torch.isfinite(out.float()).all()
+    ws = A.attention_workspace(out.device, 1, 1, 16, 1, 1)
+    cycles = A.reprojection_cycles(ws)
+    subs = sum((s + 15) // 16 for s in w.seq_lens)
+    units = ((subs + 7) // 8 + 1) // 2
+    pairs = torch.cuda.get_device_properties(0).multi_processor_count // 2
+    rounds = -(-units * OPT_13B.num_heads // pairs)
+    need = rounds * (OPT_13B.hidden // 64) * 512
+    assert need <= cycles <= 1.5 * need + 200_000, (cycles, need)
+
+
 def test_bounded_wait_that_runs_out_marks_the_output():
     """A wait nobody satisfies gives up after its clock budget and leaves code 7; the
     combine step then writes NaN instead of numbers; the next call works as before."""
