@@ -145,16 +145,16 @@ def test_hybrid_small(dtype):
     assert_close(out, ref, f"hybrid small {dtype}")
 
 
-@pytest.mark.parametrize("bs", [32, 64])
-def test_hybrid_larger_cache_blocks(bs):
+@pytest.mark.parametrize("bs,heads,head_dim", [(32, 2, 128), (64, 2, 128), (32, 4, 64)])
+def test_hybrid_larger_cache_blocks(bs, heads, head_dim):
     """Cache blocks of 32 / 64 tokens: a hidden request's 16-row sub-blocks then sit at offsets
     inside a block, K/V groups likewise."""
-    shape = LayerShape("t", 2, 128, 256, torch.float16, block_size=bs)
+    shape = LayerShape("t", heads, head_dim, 256, torch.float16, block_size=bs)
     lens, hid = [5, 40, 17, 129, 300, 64, 65], [True, False, True, False, True, True, False]
     w = make_decode_workload(shape, lens, hid, seed=4)
     ref = oracle_out(w)
     out = gpu_hybrid(w.to("cuda"))
-    assert_close(out, ref, f"hybrid, block size {bs}")
+    assert_close(out, ref, f"hybrid, block size {bs}, {heads} x {head_dim}")
 
 
 @pytest.mark.parametrize("hidden_fraction", [0.0, 1.0])
