@@ -599,6 +599,8 @@ def run_ours(args):
     if work["t_hidden"] > 0 and shape.dtype != torch.float32:
         roof_hidden.update(tensor_cycle_block(st, shape, lens, hid, tp))
 
+    per_rank = per_rank_block(st, res, tp, dev, B, shape) if tp > 1 else None
+
     out_shape = (B, shape.hidden) if tp > 1 else tuple(w.query.shape)
     e2e = EndToEnd(st, dev, tp, out_shape, shape.dtype)
     e2e_s = e2e.run(K, timer.barrier)
@@ -810,12 +812,45 @@ def run_ours(args):
     }
     if check is not None:
         line["tp_check"] = check
+    if per_rank is not None:
+        line["per_rank"] = per_rank
     line.update(line_extra)
     if cpu_baseline is not None:
         line["cpu_baseline"] = cpu_baseline
     print(json.dumps(line))
     if tp > 1:
         torch.distributed.destroy_process_group()
+
+
+def per_rank_block(st, res, tp, dev, batch, shape):
+    """What every rank measured for its own two attention kernels in the timed region, the
+    re-projection kernel's cycle count per rank, and the all-reduce of the step's [B, E] tensor
+    timed alone (20 back-to-back calls): the step is as long as its slowest rank plus the
+    exchange, and the ranks' GPUs do not sit at the same clock under the power cap."""
+    import torch.distributed as dist
+    mine = torch.tensor([res["hid_ms"], res["kv_ms"], float(st.A.reprojection_cycles(st.workspace))],
+                        device=dev, dtype=torch.float64)
+    allr = [torch.empty_like(mine) for _ in range(tp)]
+    dist.all_gather(allr, mine)
+    y = torch.zeros(batch, shape.hidden, device=dev, dtype=shape.dtype)
+    reduce = (lambda: st.tp_comm.all_reduce(y)) if st.tp_comm is not None else (lambda: dist.all_reduce(y, group=st.tp_group))
+    for _ in range(5):
+        reduce()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(20):
+        reduce()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / 20], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return {"reprojection_ms": [round(float(x[0]), 4) for x in allr],
+            "kv_path_ms": [round(float(x[1]), 4) for x in allr],
+            "reprojection_sm_cycles_cta0": [int(x[2]) for x in allr],
+            "all_reduce_alone_ms": round(float(t.item()), 4),
+            "all_reduce_bytes": int(y.numel() * y.element_size())}
 
 
 def tensor_cycle_block(st, shape, lens, hid, tp):
