@@ -149,6 +149,7 @@ bool hidden_simt_supported(int dtype, int head_size) {
 }
 
 int launch_hidden_simt(const WorkspacePtrs& ws, const SimtHiddenArgs& a, cudaStream_t stream) {
+  ScopedProfile prof(1, stream);   // the same timing hook as the tensor-core re-projection
   switch (a.dtype) {
     case APS_F32: return launch_by_head<float>(ws, a, stream);
     case APS_F16: return launch_by_head<__half>(ws, a, stream);

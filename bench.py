@@ -598,6 +598,12 @@ def run_ours(args):
     roof_hidden, roof_kv = kernel_rooflines(work, res, peaks)
     if work["t_hidden"] > 0 and shape.dtype != torch.float32:
         roof_hidden.update(tensor_cycle_block(st, shape, lens, hid, tp))
+    if shape.dtype == torch.float32:
+        # fp32 runs the CUDA-core re-projection (tcgen05 has no fp32 MMA): the tensor peak is not its bound
+        roof_hidden.update({"kernel": "hidden_simt_kernel (fp32 CUDA-core re-projection + softmax partials)",
+                            "bound": "fp32 CUDA cores (no measured peak on file)", "peak": None, "frac": None,
+                            "frac_of_burst_peak": None, "peak_source": None})
+        roof_kv["kernel"] = "kv_attention_kernel (K/V streaming, CUDA-core arithmetic: fp32)"
 
     per_rank = per_rank_block(st, res, tp, dev, B, shape) if tp > 1 else None
 
