@@ -803,10 +803,16 @@ int make_map(CUtensorMap* map, const void* base, int dtype, uint64_t cols, uint6
   return cached_tensor_map(map, spec, what);
 }
 
-// Work-order group sizes (tile pairs x heads).  4 x 10: of the orders that cost the same cycles
-// (the kernel is tensor-bound in all of them) the one that reads least from HBM (ncu, 16-request
-// case: 2.6 GB per launch against 3.4 GB for 8 x 8 and 6.3 GB for 16 x 4), i.e. spends the fewest
-// watts beside the tensor cores.
+// Work-order group sizes (tile pairs x heads).  Every order costs the same cycles (the kernel is
+// tensor-bound in all of them) and, at the power cap, the same time within a percent; what
+// differs is how much of W and of the hidden rows L2 still holds when they are needed again, i.e.
+// the DRAM traffic - and that differs more between GPUs than between orders (OPT-13B layer, ncu,
+// same binary and inputs: 4 x 10 reads 7.6 GB per launch on one B200, 9.6 GB on a second, 13.0 GB
+// on a third; 2 x 10 reads 5.8 GB on the first and 15.0 GB on the third).  About 60 MB of L2
+// serve a working set that both dies read, and the live set here (the group's W rows, 26 MB, plus
+// the rows of the tile pairs in flight, 20 - 30 MB) sits at that edge.  4 x 10 is the order all
+// the published timings were taken with; orders with fewer heads per group (W smaller, rows
+// re-read more often) or with all heads in one group (W no longer resident) read 1.5 - 2.5 x more.
 void raster_sizes(int* units, int* heads) {
   *units = 4; *heads = 10;
 #ifdef APS_TUNING

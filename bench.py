@@ -761,7 +761,9 @@ def run_ours(args):
         roofline["traffic_source"] = (capture % "hidden_path" + "9.61 + 0.037 GB and 9.47 + 0.033 GB read + written, 8.9 x the "
                                       "mandatory bytes (hidden rows and W once: 1.08 GB): W and the hidden rows are re-streamed "
                                       "from HBM per round of work items, 1.2 TB/s = 18 % of the copy bandwidth; the figure moves "
-                                      "with the box (7.4 GB and 9.5 - 10.5 GB on two others), the kernel's time does not")
+                                      "with the GPU (7.4 - 7.6 GB, 9.3 - 10.5 GB and 13.0 GB on others for the same binary and "
+                                      "inputs: the live set sits at the ~60 MB of L2 that serve data read from both dies), the "
+                                      "kernel's time x clock does not")
         roof_kv["traffic"] = 2_040_000_000
         roof_kv["traffic_source"] = capture % "kv_attention_tma" + "2.02 + 0.02 GB, 1.02 x the algorithmic bytes"
     else:
