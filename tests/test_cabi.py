@@ -75,6 +75,15 @@ def test_argument_validation_returns_status_codes():
     assert st == N.APS_ERR_UNSUPPORTED
 
 
+def test_status_and_cycle_readers_check_their_pointers():
+    lib = N.lib()
+    host = ctypes.c_ulonglong(0)
+    assert lib.aps_reprojection_cycles(0, ctypes.addressof(host), 0) == N.APS_ERR_NULL_POINTER
+    assert lib.aps_attention_status(0, ctypes.addressof(host), 0) == N.APS_ERR_NULL_POINTER
+    buf = (ctypes.c_char * 512)()
+    assert lib.aps_reprojection_cycles(ctypes.addressof(buf), 0, 0) == N.APS_ERR_NULL_POINTER
+
+
 def test_python_shims_refuse_cpu_tensors_and_map_errors():
     from apt_serve_b200 import mixed_cache_ops, ops
     z = torch.zeros(2, 8)
