@@ -42,6 +42,8 @@ PROTOTYPES = {
     "aps_prefill_cache_write": (c_int, [c_void_p] * 8 + [c_int64, c_void_p, c_int64] + [c_int] * 4 +
                                 [c_int64] * 5 + [c_int, c_void_p]),
     "aps_copy_blocks": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int64, c_void_p]),
+    "aps_swap_blocks": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
+                                c_int64, c_int, c_void_p, c_void_p]),
     "aps_attention_workspace_bytes": (c_size_t, [c_int] * 5),
     "aps_paged_decode_attention": (c_int, [c_void_p] * 6 + [c_int] * 5 + [c_int64] * 3 +
                                    [c_float, c_void_p, c_size_t, c_int, c_void_p]),

@@ -615,6 +615,52 @@ extern "C" int aps_cache_ops_status(int* host_status, void* stream) {
   return APS_OK;
 }
 
+// Block moves between one plane of a GPU cache and one plane of the pinned CPU cache (or
+// between two device caches): plain copies on the stream, issued from a native loop, with
+// every run of pairs whose source and destination blocks are both consecutive merged into
+// one copy (a swapped-out request's blocks are mostly allocated in runs).
+extern "C" int aps_swap_blocks(const void* src, void* dst, const int64_t* pairs_host, int64_t num_pairs,
+                               int64_t block_bytes, int64_t src_block_stride_bytes,
+                               int64_t dst_block_stride_bytes, int64_t src_num_blocks,
+                               int64_t dst_num_blocks, int kind, int64_t* copies_issued, void* stream) {
+  APS_REQUIRE(num_pairs >= 0 && block_bytes > 0, APS_ERR_SHAPE, "swap_blocks: bad sizes");
+  if (copies_issued != nullptr) *copies_issued = 0;
+  if (num_pairs == 0) return APS_OK;
+  APS_REQUIRE(src != nullptr && dst != nullptr && pairs_host != nullptr, APS_ERR_NULL_POINTER,
+              "swap_blocks: null pointer");
+  APS_REQUIRE(src_block_stride_bytes >= block_bytes && dst_block_stride_bytes >= block_bytes, APS_ERR_SHAPE,
+              "swap_blocks: block stride shorter than a block");
+  cudaMemcpyKind k;
+  switch (kind) {
+    case 0: k = cudaMemcpyHostToDevice; break;
+    case 1: k = cudaMemcpyDeviceToHost; break;
+    case 2: k = cudaMemcpyDeviceToDevice; break;
+    default: return fail(APS_ERR_SHAPE, "swap_blocks: kind must be 0 (host to device), 1 (device to host) or 2");
+  }
+  for (int64_t i = 0; i < num_pairs; ++i) {
+    const int64_t sb = pairs_host[2 * i], db = pairs_host[2 * i + 1];
+    APS_REQUIRE(sb >= 0 && sb < src_num_blocks && db >= 0 && db < dst_num_blocks, APS_ERR_SHAPE,
+                "swap_blocks: pair %lld (%lld -> %lld) is outside the caches", (long long)i, (long long)sb,
+                (long long)db);
+  }
+  // runs can only be merged when blocks lie back to back in both tensors
+  const bool dense = src_block_stride_bytes == block_bytes && dst_block_stride_bytes == block_bytes;
+  int64_t issued = 0;
+  for (int64_t i = 0; i < num_pairs;) {
+    int64_t run = 1;
+    while (dense && i + run < num_pairs && pairs_host[2 * (i + run)] == pairs_host[2 * i] + run &&
+           pairs_host[2 * (i + run) + 1] == pairs_host[2 * i + 1] + run)
+      ++run;
+    const char* s = static_cast<const char*>(src) + pairs_host[2 * i] * src_block_stride_bytes;
+    char* d = static_cast<char*>(dst) + pairs_host[2 * i + 1] * dst_block_stride_bytes;
+    APS_CUDA(cudaMemcpyAsync(d, s, (size_t)(run * block_bytes), k, (cudaStream_t)stream));
+    ++issued;
+    i += run;
+  }
+  if (copies_issued != nullptr) *copies_issued = issued;
+  return APS_OK;
+}
+
 extern "C" int aps_reshape_and_cache(const void* key, const void* value, void* key_cache,
                                      void* value_cache, const int64_t* slot_mapping,
                                      int64_t num_tokens, int num_heads, int head_size,

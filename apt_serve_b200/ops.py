@@ -106,10 +106,32 @@ def copy_blocks(key_caches: List[torch.Tensor], value_caches: List[torch.Tensor]
                                         N.current_stream(dev)))
 
 
-def swap_blocks(src: torch.Tensor, dst: torch.Tensor, src_to_dst: torch.Tensor) -> None:
-    """GPU <-> pinned-CPU block moves (aptserve_flash_attn.py:44-56).  PCIe-bound
-    memcpy glue, outside the rewritten kernels: one async copy per pair on the
-    current stream, like the third-party op it stands in for."""
-    pairs = src_to_dst.tolist()
-    for s, d in pairs:
-        dst[d].copy_(src[s], non_blocking=True)
+def swap_blocks(src: torch.Tensor, dst: torch.Tensor, src_to_dst: torch.Tensor) -> int:
+    """GPU <-> pinned-CPU block moves (aptserve_flash_attn.py:44-56): ``dst[d] = src[s]`` for
+    every row ``(s, d)`` of ``src_to_dst`` (a CPU int64 tensor, as the reference passes it).
+    ``src`` / ``dst`` are one plane ``[NB, BS, H, D]`` of a cache.  The copies are enqueued on the
+    current stream of the CUDA side from a native loop (``aps_swap_blocks``), runs of consecutive
+    blocks as one copy.  Returns the number of copies issued."""
+    if src.is_cuda and dst.is_cuda:
+        kind, dev = 2, src.device
+    elif src.is_cuda:
+        kind, dev = 1, src.device
+    elif dst.is_cuda:
+        kind, dev = 0, dst.device
+    else:
+        raise RuntimeError("swap_blocks: one side must be a CUDA tensor (there is no CPU path)")
+    if src.dtype != dst.dtype or src.shape[1:] != dst.shape[1:]:
+        raise RuntimeError("swap_blocks: the two caches must hold blocks of the same shape and type")
+    if not (src[0].is_contiguous() and dst[0].is_contiguous()):
+        raise RuntimeError("swap_blocks: blocks must be contiguous")
+    pairs = src_to_dst.detach().to("cpu", torch.int64).contiguous()
+    if pairs.numel() == 0:
+        return 0
+    es = src.element_size()
+    issued = ctypes.c_int64(0)
+    with torch.cuda.device(dev):
+        N.check(N.lib().aps_swap_blocks(
+            src.data_ptr(), dst.data_ptr(), pairs.data_ptr(), pairs.size(0), src[0].numel() * es,
+            src.stride(0) * es, dst.stride(0) * es, src.size(0), dst.size(0), kind,
+            ctypes.addressof(issued), N.current_stream(dev)))
+    return issued.value

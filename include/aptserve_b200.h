@@ -143,6 +143,20 @@ int aps_prefill_cache_write(const void* key, const void* value, const void* hidd
                             int64_t slot_stride, int dtype, void* stream);
 
 /*
+ * Replaces vllm._custom_ops.swap_blocks as called at fa.py:44-56 (once per layer and plane):
+ *   dst[d] = src[s] for every row (s, d) of the HOST array pairs_host [num_pairs, 2],
+ * src / dst being one plane [num_blocks, BS, H, D] of a GPU cache or of the pinned CPU
+ * cache.  kind: 0 = host to device (swap in), 1 = device to host (swap out), 2 = device to
+ * device.  Copies are enqueued on `stream` from a native loop; runs of pairs whose source and
+ * destination blocks are both consecutive become one copy.  copies_issued (may be NULL)
+ * receives the number of copies enqueued.
+ */
+int aps_swap_blocks(const void* src, void* dst, const int64_t* pairs_host, int64_t num_pairs,
+                    int64_t block_bytes, int64_t src_block_stride_bytes, int64_t dst_block_stride_bytes,
+                    int64_t src_num_blocks, int64_t dst_num_blocks, int kind, int64_t* copies_issued,
+                    void* stream);
+
+/*
  * Replaces vllm._custom_ops.copy_blocks as called at fa.py:58-65:
  * for every layer l and every row (src, dst) of block_mapping [num_pairs, 2]:
  *   key_caches[l][dst] = key_caches[l][src]; value_caches[l][dst] = value_caches[l][src].

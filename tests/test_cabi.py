@@ -75,6 +75,22 @@ def test_argument_validation_returns_status_codes():
     assert st == N.APS_ERR_UNSUPPORTED
 
 
+def test_swap_blocks_argument_checks():
+    lib = N.lib()
+    buf = (ctypes.c_char * 4096)()
+    p = ctypes.addressof(buf)
+    pairs = (ctypes.c_int64 * 4)(0, 1, 5, 0)
+    n = ctypes.c_int64(-1)
+    # nothing to do: no copy, no device needed
+    assert lib.aps_swap_blocks(p, p, ctypes.addressof(pairs), 0, 256, 256, 256, 4, 4, 1, ctypes.addressof(n), 0) == N.APS_OK
+    assert n.value == 0
+    # a block id outside the source, an unknown direction, a stride shorter than a block
+    assert lib.aps_swap_blocks(p, p, ctypes.addressof(pairs), 2, 256, 256, 256, 4, 4, 1, 0, 0) == N.APS_ERR_SHAPE
+    assert lib.aps_swap_blocks(p, p, ctypes.addressof(pairs), 1, 256, 256, 256, 4, 4, 5, 0, 0) == N.APS_ERR_SHAPE
+    assert lib.aps_swap_blocks(p, p, ctypes.addressof(pairs), 1, 256, 128, 256, 4, 4, 1, 0, 0) == N.APS_ERR_SHAPE
+    assert lib.aps_swap_blocks(0, p, ctypes.addressof(pairs), 1, 256, 256, 256, 4, 4, 1, 0, 0) == N.APS_ERR_NULL_POINTER
+
+
 def test_status_and_cycle_readers_check_their_pointers():
     lib = N.lib()
     host = ctypes.c_ulonglong(0)

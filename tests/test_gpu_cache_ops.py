@@ -166,6 +166,35 @@ def test_swap_blocks_roundtrip():
     assert torch.equal(back[1, 2].cpu(), src[1, 1].cpu())
 
 
+def test_swap_blocks_merges_runs_and_matches_the_oracle():
+    """Swap-out then swap-in of a block list with runs (consecutive source AND destination ids
+    become one copy), against the oracle's block moves, both planes."""
+    src = rand(2, 12, 16, 2, 64, dtype=torch.float16, seed=6)
+    host_ref = torch.zeros(2, 10, 16, 2, 64, dtype=torch.float16)
+    pairs = torch.tensor([[0, 3], [1, 4], [2, 5], [7, 0], [9, 9], [10, 1], [11, 2]])
+    for plane in range(2):
+        O.swap_blocks(src[plane], host_ref[plane], pairs)
+    dev = src.cuda()
+    host = torch.zeros_like(host_ref).pin_memory()
+    issued = [ops.swap_blocks(dev[plane], host[plane], pairs) for plane in range(2)]
+    torch.cuda.synchronize()
+    assert issued == [4, 4]          # runs 0-2 -> 3-5, 7 -> 0, 9 -> 9, 10-11 -> 1-2
+    assert torch.equal(bits(host), bits(host_ref))
+    back = torch.zeros_like(dev)
+    back_pairs = torch.tensor([[3, 6], [4, 7], [5, 8], [0, 0]])
+    n = ops.swap_blocks(host[0], back[0], back_pairs)
+    torch.cuda.synchronize()
+    assert n == 2
+    assert torch.equal(back[0, 6:9].cpu(), src[0, 0:3]) and torch.equal(back[0, 0].cpu(), src[0, 7])
+    # device to device, and a pair outside the destination is refused before anything is copied
+    other = torch.zeros_like(dev)
+    assert ops.swap_blocks(dev[1], other[1], torch.tensor([[2, 2], [3, 3]])) == 1
+    torch.cuda.synchronize()
+    assert torch.equal(other[1, 2:4].cpu(), src[1, 2:4])
+    with pytest.raises(RuntimeError):
+        ops.swap_blocks(dev[0], host[0], torch.tensor([[0, 10]]))
+
+
 def test_full_size_prefill_write_roundtrip():
     """Config-3-sized prefill write (OPT-13B rows): write every token of 8 long
     prompts into hidden or K/V blocks, gather the hidden rows back and compare
