@@ -119,7 +119,12 @@ def swap_blocks(src: torch.Tensor, dst: torch.Tensor, src_to_dst: torch.Tensor) 
     elif dst.is_cuda:
         kind, dev = 0, dst.device
     else:
-        raise RuntimeError("swap_blocks: one side must be a CUDA tensor (there is no CPU path)")
+        # both sides in host memory (the cache engine's bookkeeping exercised without a GPU):
+        # a host copy per pair, no device work to enqueue
+        pairs = src_to_dst.tolist()
+        for s_id, d_id in pairs:
+            dst[d_id].copy_(src[s_id])
+        return len(pairs)
     if src.dtype != dst.dtype or src.shape[1:] != dst.shape[1:]:
         raise RuntimeError("swap_blocks: the two caches must hold blocks of the same shape and type")
     if not (src[0].is_contiguous() and dst[0].is_contiguous()):
